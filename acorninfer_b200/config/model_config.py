@@ -208,6 +208,7 @@ class LatentAttentionConfig:
     scaling: RotaryScaling | None = None
     window: int | None = None    # a query sees itself and the window - 1 tokens before it
     kv_from: int | None = None   # layer whose cached latent and key part this layer reads
+    q_rank: int | None = None    # size of a latent the queries come through (None: projected directly)
 
     @classmethod
     def from_dict(cls, m: dict, where: str) -> "LatentAttentionConfig":
@@ -221,7 +222,7 @@ class LatentAttentionConfig:
             scaling=None if sc is None else RotaryScaling(_take(sc, "factor", float), _take(sc, "original", int),
                                                           _take(sc, "fast", float), _take(sc, "slow", float)),
             window=None if mask is None else _take(mask, "size", int),
-            kv_from=_take(m, "kv_from", int, None))
+            kv_from=_take(m, "kv_from", int, None), q_rank=_take(m, "q_rank", int, None))
 
     def to_dict(self) -> dict:
         rot: dict = {"base": self.rot_base, "dims": self.rot_dims}
@@ -233,6 +234,8 @@ class LatentAttentionConfig:
             out["mask"] = {"size": self.window}
         if self.kv_from is not None:
             out["kv_from"] = self.kv_from
+        if self.q_rank is not None:
+            out["q_rank"] = self.q_rank
         return out
 
 
@@ -595,6 +598,175 @@ class VagulornConfig(ModelConfig):
         if self.eos_token_id:
             out["eos_token_id"] = list(self.eos_token_id)
         return out
+
+
+# --------------------------------------------------------------------------- Tedenex
+
+
+@dataclass(frozen=True)
+class ConvAttentionConfig:
+    """Grouped-query attention with biased projections, a short convolution over time on q, k and v, q/k norm,
+    no rotation, a penalty per head on the distance to the key and, with ``mask_size``, blocks of positions."""
+
+    kind: ClassVar[str] = "attention"
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    conv: int | None = None
+    mask_size: int | None = None
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "ConvAttentionConfig":
+        mask = _sub(m, "mask", where, required=False)
+        return cls(heads=_take(m, "heads", int), kv_heads=_take(m, "kv_heads", int), dim=_take(m, "dim", int),
+                   vdim=_take(m, "vdim", int), scale=_take(m, "scale", float), conv=_take(m, "conv", int, None),
+                   mask_size=None if mask is None else _take(mask, "size", int, None))
+
+    def check(self, where: str) -> None:
+        if min(self.heads, self.kv_heads, self.dim, self.vdim) < 1 or self.heads % self.kv_heads:
+            raise ConfigError(f"config.json: {where}sizes must be >= 1 and 'heads' a multiple of 'kv_heads'")
+        if self.conv is not None and self.conv < 1:
+            raise ConfigError(f"config.json: {where}conv must be >= 1, got {self.conv}")
+        if self.mask_size is not None and self.mask_size < 1:
+            raise ConfigError(f"config.json: {where}mask.size must be >= 1, got {self.mask_size}")
+
+    def to_dict(self) -> dict:
+        out: dict = {"dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "scale": self.scale, "vdim": self.vdim}
+        if self.conv is not None:
+            out["conv"] = self.conv
+        if self.mask_size is not None:
+            out["mask"] = {"size": self.mask_size}
+        return out
+
+
+@dataclass(frozen=True)
+class TimeMixConfig:
+    """Time mixing with a matrix state per head.  ``decay_rank``, the inner size of the decay's low-rank
+    projection, is fixed by a checkpoint's tensors; it is needed (and written) only to make a model from nothing."""
+
+    kind: ClassVar[str] = "wkv"
+    heads: int
+    dim: int
+    decay_rank: int | None = None
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "TimeMixConfig":
+        return cls(heads=_take(m, "heads", int), dim=_take(m, "dim", int), decay_rank=_take(m, "decay_rank", int, None))
+
+    def check(self, where: str) -> None:
+        if min(self.heads, self.dim) < 1 or (self.decay_rank is not None and self.decay_rank < 1):
+            raise ConfigError(f"config.json: {where}sizes must be >= 1")
+
+    def to_dict(self) -> dict:
+        out = {"dim": self.dim, "heads": self.heads}
+        if self.decay_rank is not None:
+            out["decay_rank"] = self.decay_rank
+        return out
+
+
+@dataclass(frozen=True)
+class LayerLoop:
+    """Layers ``start .. stop - 1`` run ``times`` times in a row with the same weights."""
+
+    start: int
+    stop: int
+    times: int
+
+
+@dataclass(frozen=True)
+class TedenexLayer:
+    type: str                   # "attention", "wkv" or "latent_attention"
+    mixer: "ConvAttentionConfig | TimeMixConfig | LatentAttentionConfig"
+    ff: int | None              # inner width of the dense feed-forward; None: the layer has none
+
+
+@dataclass(frozen=True)
+class TedenexConfig(ModelConfig):
+    """Tedenex: layers ``x += norm(mixer(norm(x))); x += norm(ff(norm(x)))`` (RMS norms whose weights are stored
+    as distances from one) followed by a token's side rows, with a mixer that is convolved attention in blocks of
+    positions, time mixing with a matrix state, or attention through cached latents; a span of the layers may run
+    several times in a row, each pass with a cache of its own, the token rows added again before each pass but the
+    first; a final norm and the token table as output matrix.  ``config.json`` lists the layers in order."""
+
+    architecture: ClassVar[str] = "Tedenex"
+
+    vocab_size: int
+    hidden_size: int
+    norm_eps: float
+    layers: tuple[TedenexLayer, ...]
+    loop: LayerLoop | None = None
+    side_dim: int | None = None
+    eos_token_id: tuple[int, ...] = field(default_factory=tuple)
+
+    def __post_init__(self) -> None:
+        if self.vocab_size < 1 or self.hidden_size < 1 or not self.layers:
+            raise ConfigError("config.json: 'vocab', 'width' must be >= 1 and 'layers' non-empty")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm 'eps' must be > 0, got {self.norm_eps}")
+        if self.side_dim is not None and self.side_dim < 1:
+            raise ConfigError(f"config.json: token_side 'dim' must be >= 1, got {self.side_dim}")
+        if self.loop is not None:
+            lp = self.loop
+            if not (0 <= lp.start < lp.stop <= len(self.layers)) or lp.times < 1:
+                raise ConfigError(f"config.json: loop must name layers start < stop <= {len(self.layers)} and times >= 1, "
+                                  f"got start {lp.start}, stop {lp.stop}, times {lp.times}")
+        for i, layer in enumerate(self.layers):
+            m, w = layer.mixer, f"layers[{i}].mixer."
+            if isinstance(m, LatentAttentionConfig):
+                if min(m.heads, m.dim, m.vdim, m.kv_rank) < 1 or m.rot_dim < 0 or (m.q_rank is not None and m.q_rank < 1):
+                    raise ConfigError(f"config.json: {w}sizes must be >= 1")
+                if m.rot_dims % 2 or not (0 <= m.rot_dims <= m.rot_dim):
+                    raise ConfigError(f"config.json: {w}rot.dims must be even and at most rot_dim, got {m.rot_dims}")
+                if m.kv_from is not None or m.scaling is not None or m.window is not None:
+                    raise ConfigError(f"config.json: {w}kv_from, rot.scaling and mask are not part of this architecture")
+            else:
+                m.check(w)
+            if layer.ff is not None and layer.ff < 1:
+                raise ConfigError(f"config.json: layers[{i}].mlp.ff must be >= 1, got {layer.ff}")
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "TedenexConfig":
+        layers_raw = raw.get("layers")
+        if not isinstance(layers_raw, list) or not layers_raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, lr in enumerate(layers_raw):
+            where = f"layers[{i}]."
+            kind = lr.get("type") if isinstance(lr, dict) else None
+            if kind not in _TEDENEX_MIXERS:
+                raise ConfigError(f"config.json: {where}'type' must be one of {sorted(_TEDENEX_MIXERS)}, got {kind!r}")
+            mixer = _TEDENEX_MIXERS[kind].from_dict(_sub(lr, "mixer", where), where + "mixer.")
+            mlp = _sub(lr, "mlp", where, required=False)
+            if mlp is not None and mlp.get("kind", "dense") != "dense":
+                raise ConfigError(f"config.json: {where}mlp.kind must be 'dense', got {mlp.get('kind')!r}")
+            layers.append(TedenexLayer(kind, mixer, None if mlp is None else _take(mlp, "ff", int)))
+        loop = _sub(raw, "loop", "", required=False)
+        side = _sub(raw, "token_side", "", required=False)
+        eos = raw.get("eos_token_id")
+        eos_ids = () if eos is None else tuple(int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos]))
+        return cls(vocab_size=_take(raw, "vocab", int), hidden_size=_take(raw, "width", int),
+                   norm_eps=_take(_sub(raw, "norm", ""), "eps", float), layers=tuple(layers),
+                   loop=None if loop is None else LayerLoop(_take(loop, "start", int), _take(loop, "stop", int),
+                                                            _take(loop, "times", int)),
+                   side_dim=None if side is None else _take(side, "dim", int), eos_token_id=eos_ids)
+
+    def to_dict(self) -> dict:
+        out: dict = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+                     "norm": {"eps": self.norm_eps}}
+        out["layers"] = [{"type": l.type, "mixer": l.mixer.to_dict(),
+                          "mlp": None if l.ff is None else {"ff": l.ff, "kind": "dense"}} for l in self.layers]
+        if self.loop is not None:
+            out["loop"] = {"start": self.loop.start, "stop": self.loop.stop, "times": self.loop.times}
+        if self.side_dim is not None:
+            out["token_side"] = {"dim": self.side_dim}
+        if self.eos_token_id:
+            out["eos_token_id"] = list(self.eos_token_id)
+        return out
+
+
+_TEDENEX_MIXERS = {"attention": ConvAttentionConfig, "wkv": TimeMixConfig, "latent_attention": LatentAttentionConfig}
 
 
 def read_config_json(model_dir: str | Path) -> dict:

@@ -37,6 +37,7 @@ struct DecodeParams {
     int table_stride, nq, nkv, logP, num_splits;
     AttnMask mask;           // attention_mask.cuh: window, blocks of positions, kept first keys
     float scale_log2;         // softmax scale * log2(e)
+    const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
 };
 
 template <int D>
@@ -85,6 +86,11 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float slope_log2[2] = {0.f, 0.f};                      // of the query heads in rows g and g + 8
+    if (p.slopes) {
+        if (g < rep) slope_log2[0] = p.slopes[kvh * rep + g] * 1.4426950408889634f;
+        if (g + 8 < rep) slope_log2[1] = p.slopes[kvh * rep + g + 8] * 1.4426950408889634f;
+    }
 
     auto load_chunk = [&](int c, int stage) {
         if (c < c1)
@@ -122,7 +128,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int key = wkey0 + j * 8 + 2 * tq + (e & 1);
-                    s[j][e] = key < hi ? s[j][e] * p.scale_log2 : -INFINITY;
+                    s[j][e] = key < hi ? fmaf(s[j][e], p.scale_log2, -slope_log2[e >> 1] * (float)(pos - mask_key(key, vlo, lo)))
+                                       : -INFINITY;
                     mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
                 }
             float corr[2];
@@ -274,7 +281,7 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
                                       int table_stride, const int* token_row, const int* positions,
                                       const int* token_list, int n, int nq, int nkv, int d, int P, float scale,
                                       int window, int num_splits, float* part_o, float* part_lse,
-                                      int chunk, int keep, cudaStream_t stream) {
+                                      int chunk, int keep, const float* slopes, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (!acorn_attention_decode_supported(nq, nkv, d) || num_splits < 1 || num_splits > DEC_MAX_SPLITS || n > 65535)
         return ACORN_ERR_UNSUPPORTED;
@@ -288,6 +295,7 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
     if (p.logP < 0) return ACORN_ERR_UNSUPPORTED;   // page sizes are powers of two
     p.mask = AttnMask{window, chunk, keep}; p.num_splits = num_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.slopes = slopes;
     int rc;
     switch (d) {
         case 16: rc = launch_decode<16>(p, n, stream); break;

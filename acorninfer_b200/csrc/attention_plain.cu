@@ -12,7 +12,8 @@
 // Values may be narrower than keys (dv <= d: the first dv elements of a value row are summed, the
 // output is [tokens, nq, dv]), which also serves a cache whose value rows are the key rows' heads
 // (v_pages == k_pages).  `sink` (one float per query head, or null) adds exp(sink) to the softmax
-// denominator.
+// denominator.  `slopes` (one float per query head, or null) takes slope_h * (query position - key position)
+// off every score.
 //
 // A chunk is 512 keys.  Scores: one thread a key, the dot products of all the block's query heads
 // in one pass over the key row (the rows reach the threads through a hand-over in shared memory, so
@@ -33,7 +34,8 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     const T* __restrict__ q, int64_t q_stride, T* __restrict__ out, const T* __restrict__ k_pages,
     const T* __restrict__ v_pages, const int* __restrict__ block_table, const int* __restrict__ page_base,
     int table_stride, const int* __restrict__ token_row, const int* __restrict__ positions, int nq, int nkv, int d,
-    int P, float scale, AttnMask mask, int parts, int dv, int v_row, const float* __restrict__ sink, int hpb) {
+    int P, float scale, AttnMask mask, int parts, int dv, int v_row, const float* __restrict__ sink, int hpb,
+    const float* __restrict__ slopes) {
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                                   // [heads][d], scaled
     float* sc = smem + PLAIN_HEADS * d;                 // [heads][PLAIN_THREADS] probabilities of the chunk
@@ -136,9 +138,11 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
                     for (int g = 0; g < PLAIN_HEADS; ++g)
                         if (g < G) dot[g] += qs[g * d + i] * kv;
                 }
+                // a slope per head on the distance to the key, taken off the score
+                const float dist = (float)(pos - mask_key(j, vlo, lo));
 #pragma unroll
                 for (int g = 0; g < PLAIN_HEADS; ++g)
-                    if (g < G) s[g] = dot[g];
+                    if (g < G) s[g] = slopes ? dot[g] - slopes[h0 + g] * dist : dot[g];
             }
         }
 #pragma unroll
@@ -239,7 +243,7 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
                                      int table_stride, const int* token_row, const int* positions,
                                      int tokens, int nq, int nkv, int d, int P, float scale, int window,
                                      int dtype, int dv, const float* sink, int chunk, int keep, int v_row,
-                                     cudaStream_t stream) {
+                                     const float* slopes, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (dv < 1 || dv > PLAIN_MAX_D || v_row < dv) return ACORN_ERR_UNSUPPORTED;
     const AttnMask mask = {window, chunk, keep};
@@ -264,6 +268,6 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
     dim3 grid(tokens, nkv * parts);
     ACORN_DISPATCH_DTYPE(dtype, T, (attention_plain_kernel<T><<<grid, PLAIN_THREADS, smem, stream>>>(
         (const T*)q, q_stride, (T*)out, (const T*)k_pages, (const T*)v_pages, block_table, page_base,
-        table_stride, token_row, positions, nq, nkv, d, P, scale, mask, parts, dv, v_row, sink, hpb)));
+        table_stride, token_row, positions, nq, nkv, d, P, scale, mask, parts, dv, v_row, sink, hpb, slopes)));
     return acorn_launch_status();
 }

@@ -33,6 +33,7 @@ struct PrefillParams {
     int table_stride, nq, nkv, logP;
     AttnMask mask;
     float scale_log2;
+    const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
 };
 
 template <int D>
@@ -55,6 +56,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
     const int vlo = mask_vlo(p.mask, lo);                    // kept first keys ride in front: virtual indices vlo .. hi-1
     const int hi = pos0 + n_q;
     const int* table = p.block_table + (int64_t)r * p.table_stride - p.page_base[r];
+    const float slope_log2 = p.slopes ? p.slopes[head] * 1.4426950408889634f : 0.f;
 
     // this warp's queries: rows g and g+8 of its 16
     const int qi0 = warp * 16 + g, qi1 = qi0 + 8;
@@ -122,8 +124,9 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
                 for (int e = 0; e < 4; ++e) {
                     const int v = key0 + j * 8 + 2 * tq + (e & 1);
                     const int qp = qpos[e >> 1];
-                    const bool ok = v < hi && mask_sees(p.mask, qp, mask_key(v, vlo, lo));
-                    s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                    const int key = mask_key(v, vlo, lo);
+                    const bool ok = v < hi && mask_sees(p.mask, qp, key);
+                    s[j][e] = ok ? fmaf(s[j][e], p.scale_log2, -slope_log2 * (float)(qp - key)) : -INFINITY;
                     mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
                 }
             float corr[2], mref[2];
@@ -206,7 +209,7 @@ extern "C" int acorn_attention_prefill(const void* q, int64_t q_stride, void* ou
                                        const void* v_pages, const int* block_table, const int* page_base,
                                        int table_stride, const int* row_start, const int* row_pos,
                                        const int* tiles, int n_tiles, int nq, int nkv, int d, int P, float scale,
-                                       int window, int chunk, int keep, cudaStream_t stream) {
+                                       int window, int chunk, int keep, const float* slopes, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!acorn_attention_prefill_supported(nq, nkv, d)) return ACORN_ERR_UNSUPPORTED;
     PrefillParams p;
@@ -217,6 +220,7 @@ extern "C" int acorn_attention_prefill(const void* q, int64_t q_stride, void* ou
     if (p.logP < 0) return ACORN_ERR_UNSUPPORTED;   // page sizes are powers of two
     p.mask = AttnMask{window, chunk, keep};
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.slopes = slopes;
     switch (d) {
         case 16: return launch_prefill<16>(p, n_tiles, stream);
         case 32: return launch_prefill<32>(p, n_tiles, stream);

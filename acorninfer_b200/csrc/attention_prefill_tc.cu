@@ -51,6 +51,7 @@ struct AttnTcParams {
     int keep;                // the request's first `keep` keys are seen whatever the window or block
     int n_tiles, pairs;      // pairs = ceil((nq / nkv) / 2): CTAs per (tile, kv head)
     float scale_log2;
+    const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
 };
 
 // shared memory map (bytes; the tile regions are 1024-aligned)
@@ -61,6 +62,14 @@ struct AttnTcParams {
 // q_full, full[SLOTS], empty[SLOTS], s_full[unit], p_full[unit], o_done[unit]
 #define ATC_NUM_BARS (1 + 2 * ATC_SLOTS + 2 + 2 + 2)
 #define ATC_TMEM_COLS 512
+
+// s[c] -= step * (qpos - (key0 + c)): a penalty on the distance to the key, in units of the raw score
+// (the slope divided by the softmax scale), so that the scaled exponent below holds it
+__device__ __forceinline__ void atc_distance(float (&s)[64], int key0, int qpos, float step) {
+    const float base = (float)(qpos - key0);
+#pragma unroll
+    for (int c = 0; c < 64; ++c) s[c] = fmaf(-step, base - (float)c, s[c]);
+}
 
 // -inf where the query at qpos may not see the key (causal, the first key its window or its block of positions
 // lets it see, the request's first `keep` keys seen whatever the rule, rows beyond the tile's queries)
@@ -284,6 +293,8 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         const uint32_t my_s = tmem_s + lane_addr + u * 128, my_o = tmem_o + lane_addr + u * 128;
         const uint32_t s_full = s_full0 + 8 * u, p_full = p_full0 + 8 * u, o_done = o_done0 + 8 * u;
         float m_ref = -INFINITY, l_run = 0.f;
+        const float dist_step = p.slopes ? p.slopes[head] * 1.4426950408889634f / p.scale_log2 : 0.f;
+        const bool sloped = p.slopes != nullptr;
         bool good = true;
         for (int j = 0; j < nb; ++j) {
             // S of block j is complete; so is P V of block j-1, issued before it: O is stable
@@ -302,10 +313,12 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             uint32_t w_lo[32], w_hi[32];
             float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
             tmem_ld64(my_s, s);
+            if (sloped) atc_distance(s, key0, qpos, dist_step);
             if (masked) atc_mask(s, key0, qpos, row_ok, first_seen, p.keep);
             float mx = atc_max(s);
             float psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             tmem_ld64(my_s + 64, s);
+            if (sloped) atc_distance(s, key0 + 64, qpos, dist_step);
             if (masked) atc_mask(s, key0 + 64, qpos, row_ok, first_seen, p.keep);
             mx = fmaxf(mx, atc_max(s)) * p.scale_log2;                   // the scale is positive
             float corr = 1.f;
@@ -319,6 +332,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
                 }
                 psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
                 tmem_ld64(my_s, s);
+                if (sloped) atc_distance(s, key0, qpos, dist_step);
                 if (masked) atc_mask(s, key0, qpos, row_ok, first_seen, p.keep);
                 psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             } else {
@@ -388,7 +402,8 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
                                           const void* v_pages, int64_t num_pages, const int* block_table,
                                           const int* page_base, int table_stride, const int* row_start,
                                           const int* row_pos, const int* tiles, int n_tiles, int nq, int nkv, int d,
-                                          int P, float scale, int window, int chunk, int keep, cudaStream_t stream) {
+                                          int P, float scale, int window, int chunk, int keep, const float* slopes,
+                                          cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!acorn_attention_prefill_tc_supported(nq, nkv, d, P) || q_stride % 8 != 0 || ((uintptr_t)q & 15))
         return ACORN_ERR_UNSUPPORTED;
@@ -396,6 +411,7 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
     p.out = (bf16*)out; p.block_table = block_table; p.page_base = page_base; p.row_start = row_start;
     p.row_pos = row_pos; p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
     p.logP = acorn_log2_exact_tc(P); p.window = window; p.chunk = chunk; p.keep = keep; p.scale_log2 = scale * 1.4426950408889634f;
+    p.slopes = slopes;
     p.n_tiles = n_tiles; p.pairs = (nq / nkv + 1) / 2;
     const int64_t ctas = (int64_t)n_tiles * nkv * p.pairs;
     if (ctas > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;

@@ -101,12 +101,13 @@ extern "C" int acorn_delta_prep(const void* main_, int64_t ld, const float* up, 
 }
 
 // The convolution's memory after the step: the last taps - 1 inputs of the request, i.e. of the old
-// memory followed by the row's inputs.  A thread owns a channel of a row, reads what it needs and
+// memory followed by the row's inputs (plus a bias per channel, if one is given).  A thread owns a channel of a row, reads what it needs and
 // only then writes, so a row shorter than the memory shifts it correctly.
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ main_, int64_t ld, float* __restrict__ state,
                                          int64_t slot_stride, int64_t conv_off, const int* __restrict__ row_start,
-                                         const int* __restrict__ row_slot, int C, int taps, int skip_single) {
+                                         const int* __restrict__ row_slot, int C, int taps, int skip_single,
+                                         const float* __restrict__ bias) {
     pdl_wait();
     pdl_trigger();
     const int r = blockIdx.y;
@@ -120,7 +121,8 @@ __global__ void conv_state_update_kernel(const T* __restrict__ main_, int64_t ld
     for (int j = 0; j < DELTA_MAX_TAPS - 1; ++j) {
         if (j < taps - 1) {
             const int idx = L + j - (taps - 1);         // index into the row's inputs; negative: old memory
-            keep[j] = idx >= 0 ? to_float(main_[(int64_t)(first + idx) * ld + c]) : cs[(int64_t)(L + j) * C + c];
+            keep[j] = idx >= 0 ? to_float(main_[(int64_t)(first + idx) * ld + c]) + (bias ? bias[c] : 0.f)
+                               : cs[(int64_t)(L + j) * C + c];
         }
     }
 #pragma unroll
@@ -130,13 +132,13 @@ __global__ void conv_state_update_kernel(const T* __restrict__ main_, int64_t ld
 
 extern "C" int acorn_conv_state_update(const void* main_, int64_t ld, float* state, int64_t slot_stride, int64_t conv_off,
                                        const int* row_start, const int* row_slot, int rows, int C, int taps, int dtype,
-                                       int skip_single, cudaStream_t stream) {
+                                       int skip_single, const float* bias, cudaStream_t stream) {
     if (rows <= 0 || taps <= 1) return 0;
     if (taps > DELTA_MAX_TAPS || rows > 65535) return ACORN_ERR_UNSUPPORTED;
     dim3 grid((C + 127) / 128, rows);
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(conv_state_update_kernel<T>, grid, dim3(128), 0, stream,
                                                        (const T*)main_, ld, state, slot_stride, conv_off, row_start,
-                                                       row_slot, C, taps, skip_single));
+                                                       row_slot, C, taps, skip_single, bias));
     return ACORN_ERR_UNSUPPORTED;
 }
 
@@ -158,12 +160,17 @@ __device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
 }
 
-template <int DPT, int DELTA_SLICES>
+//
+// PRE (a recurrence without the delta correction whose output reads the state before the token's decay and
+// write, and sees the token itself through a bonus u per head and key channel: time mixing of the RWKV kind):
+//     o = S^T q + (sum_d q[d] u[d] k[d]) v,      S[d] = g[d] S[d] + k[d] v.
+// It is the same loop with gq = q, no sum against gk, beta = 1 and the bonus inside the k . q sum.
+template <int DPT, int DELTA_SLICES, bool PRE>
 __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
     const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state, int64_t slot_stride,
     const int* __restrict__ row_start, const int* __restrict__ row_slot, float* __restrict__ out, int H, int KH, int dim,
-    int vdim, int stage) {
+    int vdim, int stage, const float* __restrict__ bonus) {
     constexpr int DELTA_COLS = DELTA_THREADS / DELTA_SLICES;           // value channels a block
     extern __shared__ __align__(16) float sm[];
     constexpr int DIMP = DPT * DELTA_SLICES;                           // dim rounded up: entries beyond dim are zero
@@ -206,7 +213,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
             if (c0 + cc < vdim) cp_async_4(dst, vv + ((int64_t)(t0 + tt) * H + h) * vdim + c0 + cc);
             else *dst = 0.f;
         }
-        if (threadIdx.x < n) cp_async_4(sb + (s & 1) * stage + threadIdx.x, beta + (int64_t)(t0 + threadIdx.x) * H + h);
+        if (!PRE && threadIdx.x < n) cp_async_4(sb + (s & 1) * stage + threadIdx.x, beta + (int64_t)(t0 + threadIdx.x) * H + h);
     };
 
     if (stages > 0) fetch(0);
@@ -223,13 +230,16 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (d < dim) {
                 const float q = rw[(tt * 3 + 0) * dim + d], k = rw[(tt * 3 + 1) * dim + d], gg = rw[(tt * 3 + 2) * dim + d];
-                v = make_float4(gg * k, gg * q, gg, k);
+                v = PRE ? make_float4(0.f, q, gg, k) : make_float4(gg * k, gg * q, gg, k);
             }
             pack[e] = v;
         }
         for (int tt = warp; tt < n; tt += DELTA_THREADS / 32) {
             float kq = 0.f;
-            for (int d = lane; d < dim; d += 32) kq = fmaf(rw[(tt * 3 + 0) * dim + d], rw[(tt * 3 + 1) * dim + d], kq);
+            for (int d = lane; d < dim; d += 32) {
+                const float qd = PRE ? rw[(tt * 3 + 0) * dim + d] * bonus[(int64_t)h * dim + d] : rw[(tt * 3 + 0) * dim + d];
+                kq = fmaf(qd, rw[(tt * 3 + 1) * dim + d], kq);
+            }
             kq = warp_sum(kq);
             if (lane == 0) skq[tt] = kq;
         }
@@ -245,18 +255,18 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
             float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT; i += 2) {
-                a0 = fmaf(S[i], e[i].x, a0);
+                if (!PRE) a0 = fmaf(S[i], e[i].x, a0);
                 b0 = fmaf(S[i], e[i].y, b0);
-                a1 = fmaf(S[i + 1], e[i + 1].x, a1);
+                if (!PRE) a1 = fmaf(S[i + 1], e[i + 1].x, a1);
                 b1 = fmaf(S[i + 1], e[i + 1].y, b1);
             }
             float a = a0 + a1, b = b0 + b1;
 #pragma unroll
             for (int o = 1; o < DELTA_SLICES; o <<= 1) {
-                a += __shfl_xor_sync(0xffffffffu, a, o);
+                if (!PRE) a += __shfl_xor_sync(0xffffffffu, a, o);
                 b += __shfl_xor_sync(0xffffffffu, b, o);
             }
-            const float u = b_s[tt] * (v_s[tt * DELTA_COLS + col] - a);
+            const float u = PRE ? v_s[tt * DELTA_COLS + col] : b_s[tt] * (v_s[tt * DELTA_COLS + col] - a);
             if (slice == 0 && live) out[((int64_t)(t0 + tt) * H + h) * vdim + column] = fmaf(skq[tt], u, b);
 #pragma unroll
             for (int i = 0; i < DPT; ++i) S[i] = fmaf(e[i].w, u, e[i].z * S[i]);
@@ -273,12 +283,18 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
 
 extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* vv, const float* beta, const float* g,
                                 float* state, int64_t slot_stride, const int* row_start, const int* row_slot, float* out,
-                                int rows, int H, int KH, int dim, int vdim, cudaStream_t stream) {
+                                int rows, int H, int KH, int dim, int vdim, const float* bonus, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H > 65535 || vdim > 65535 || dim > 256 || H % KH) return ACORN_ERR_UNSUPPORTED;
+    if (bonus == nullptr && beta == nullptr) return ACORN_ERR_UNSUPPORTED;
     dim3 block(DELTA_THREADS);
     const int stage = dim <= 64 ? 32 : (dim <= 128 ? 16 : 8);
 #define DELTA_LAUNCH(N, SL)                                                                                                   \
+    do {                                                                                                                      \
+        if (bonus) DELTA_LAUNCH_AS(N, SL, true);                                                                              \
+        DELTA_LAUNCH_AS(N, SL, false);                                                                                        \
+    } while (0)
+#define DELTA_LAUNCH_AS(N, SL, PRE)                                                                                           \
     do {                                                                                                                      \
         const int cols = DELTA_THREADS / (SL);                                                                                \
         dim3 grid(rows, H, (vdim + cols - 1) / cols);                                                                         \
@@ -286,13 +302,13 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
                             sizeof(float);                                                                                    \
         static AcornPerDevice configured;                                                                                     \
         if (!configured.seen()) {                                                                                             \
-            cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<N, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+            cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<N, SL, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                                  100 * 1024);                                                                 \
             if (e != cudaSuccess) return (int)e;                                                                              \
             configured.mark();                                                                                                \
         }                                                                                                                     \
-        return acorn_launch(delta_rule_kernel<N, SL>, grid, block, smem, stream, qn, kn, vv, beta, g, state, slot_stride,     \
-                            row_start, row_slot, out, H, KH, dim, vdim, stage);                                               \
+        return acorn_launch(delta_rule_kernel<N, SL, PRE>, grid, block, smem, stream, qn, kn, vv, beta, g, state,             \
+                            slot_stride, row_start, row_slot, out, H, KH, dim, vdim, stage, bonus);                           \
     } while (0)
     // a thread holds few state entries (4; 8 for the widest heads): a warp is alone on its scheduler, so the
     // time of a token is the number of instructions a thread issues for it, and spreading a column over more
@@ -304,18 +320,21 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
     if (dim <= 128) DELTA_LAUNCH(8, 16);
     DELTA_LAUNCH(8, 32);
 #undef DELTA_LAUNCH
+#undef DELTA_LAUNCH_AS
 }
 
-// y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * gate   (w [vdim] shared by the heads)
+// y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * gate   (w [vdim] shared by the heads: w_heads = 1; or one
+// per head, [H, vdim]: w_heads = H)
 template <typename T>
-__global__ void delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gate, const float* __restrict__ w,
-                                 T* __restrict__ y, int vdim, float eps, int64_t total_heads) {
+__global__ void delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gate, const float* __restrict__ w_,
+                                 T* __restrict__ y, int vdim, float eps, int64_t total_heads, int w_heads) {
     pdl_wait();
     pdl_trigger();
     const int lane = threadIdx.x & 31;
     const int64_t th = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // token * H + head
     if (th >= total_heads) return;
     const float* row = o + th * vdim;
+    const float* w = w_ + (th % w_heads) * vdim;
     float ss = 0.f;
     for (int j = lane; j < vdim; j += 32) ss += row[j] * row[j];
     ss = warp_sum(ss);
@@ -324,12 +343,12 @@ __global__ void delta_out_kernel(const float* __restrict__ o, const float* __res
 }
 
 extern "C" int acorn_delta_out(const float* o, const float* gate, const float* w, void* y, int tokens, int H, int vdim,
-                               float eps, int dtype, cudaStream_t stream) {
+                               float eps, int dtype, int w_per_head, cudaStream_t stream) {
     const int64_t total = (int64_t)tokens * H;
     if (total <= 0) return 0;
     const int64_t blocks = (total + 3) / 4;
     if (blocks > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(delta_out_kernel<T>, dim3((unsigned)blocks), dim3(128), 0, stream, o,
-                                                       gate, w, (T*)y, vdim, eps, total));
+                                                       gate, w, (T*)y, vdim, eps, total, w_per_head ? H : 1));
     return ACORN_ERR_UNSUPPORTED;
 }

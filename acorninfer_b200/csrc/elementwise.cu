@@ -229,6 +229,90 @@ extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int bl
     return ACORN_ERR_UNSUPPORTED;
 }
 
+// ---------------------------------------------------------------- plain activations
+// out = act(x) elementwise: 0 the square of relu, 1 tanh, 2 the tanh form of gelu, 3 silu.  float32 arithmetic,
+// one rounding.  x [rows, n] with a row stride; out contiguous.
+__device__ __forceinline__ float plain_act(float z, int act) {
+    switch (act) {
+        case 0: { const float r = fmaxf(z, 0.f); return r * r; }
+        case 1: return tanhf(z);
+        case 2: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        default: return z / (1.f + expf(-z));
+    }
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, int64_t ld, T* __restrict__ out, int n, int act) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t row = blockIdx.x;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x)
+        out[row * n + i] = from_float<T>(plain_act(to_float(x[row * ld + i]), act));
+}
+
+// bfloat16 rows of a width that is a multiple of 8 and 16-byte aligned: eight elements a thread and step
+__global__ void activation_bf16x8_kernel(const bf16* __restrict__ x, int64_t ld, bf16* __restrict__ out, int n8, int act) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t row = blockIdx.x;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n8; i += gridDim.y * blockDim.x) {
+        const uint4 in = *reinterpret_cast<const uint4*>(x + row * ld + (int64_t)i * 8);
+        const uint32_t iw[4] = {in.x, in.y, in.z, in.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&iw[k]));
+            __nv_bfloat162 o = __floats2bfloat162_rn(plain_act(f.x, act), plain_act(f.y, act));
+            ow[k] = *reinterpret_cast<uint32_t*>(&o);
+        }
+        *reinterpret_cast<uint4*>(out + (row * n8 + i) * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
+extern "C" int acorn_activation(const void* x, int64_t ld, void* out, int rows, int n, int act, int dtype,
+                                cudaStream_t stream) {
+    if (rows <= 0 || n <= 0) return 0;
+    if (act < 0 || act > 3) return ACORN_ERR_UNSUPPORTED;
+    if (dtype == ACORN_DTYPE_BF16 && n % 8 == 0 && ld % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        int by = (n / 8 + 255) / 256;
+        if (by > 64) by = 64;
+        return acorn_launch(activation_bf16x8_kernel, dim3(rows, by), dim3(256), 0, stream, (const bf16*)x, ld, (bf16*)out,
+                            n / 8, act);
+    }
+    int by = (n + 255) / 256;
+    if (by > 64) by = 64;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(activation_kernel<T>, dim3(rows, by), dim3(256), 0, stream,
+                                                       (const T*)x, ld, (T*)out, n, act));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- a token's own side rows, gated
+// out[t, i] = gelu_tanh(z[t, i]) * table[ids[t], col0 + i]: columns col0 .. col0 + n of the token's row of a
+// side table, gated by a projection z of the stream.  float32 arithmetic, one rounding.
+template <typename T>
+__global__ void side_gate_kernel(const T* __restrict__ z, const int* __restrict__ ids, const T* __restrict__ table,
+                                 int64_t ld_table, int col0, T* __restrict__ out, int64_t total, int n) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t t = idx / n;
+    const int i = (int)(idx - t * n);
+    const float e = to_float(table[(int64_t)ids[t] * ld_table + col0 + i]);
+    out[idx] = from_float<T>(plain_act(to_float(z[idx]), 2) * e);
+}
+
+extern "C" int acorn_side_gate(const void* z, const int* ids, const void* table, int64_t ld_table, int col0, void* out,
+                               int tokens, int n, int dtype, cudaStream_t stream) {
+    const int64_t total = (int64_t)tokens * n;
+    if (total <= 0) return 0;
+    const int64_t blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(side_gate_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream,
+                                                       (const T*)z, ids, (const T*)table, ld_table, col0, (T*)out, total, n));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
 // ---------------------------------------------------------------- casts
 template <typename A, typename B>
 __global__ void cast_kernel(const A* __restrict__ in, B* __restrict__ out, int64_t n) {
@@ -329,6 +413,52 @@ extern "C" int acorn_rmsnorm_add(float* resid32, const void* y, const float* w, 
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(rmsnorm_add_kernel<T>, dim3(rows), dim3(threads), 0, stream, resid32,
                                                        (const T*)y, w, (T*)rounded, H, eps));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// The same, followed at once by the norm the next sublayer reads the stream through:
+//   x = resid32[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w;   normed[t] = x * rsqrt(mean(x^2) + eps_next) * w_next
+// (a sublayer's output norm and the next sublayer's input norm in one pass over the row; the updated row
+// waits in shared memory between the two reductions).
+template <typename T>
+__global__ void rmsnorm_add_norm_kernel(float* __restrict__ resid32, const T* __restrict__ y, const float* __restrict__ w,
+                                        const float* __restrict__ w_next, T* __restrict__ normed, int H, float eps,
+                                        float eps_next) {
+    extern __shared__ float xrow[];
+    __shared__ float scratch[32];
+    pdl_wait();
+    pdl_trigger();
+    const int64_t row = blockIdx.x;
+    const T* yr = y + row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_float(yr[i]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    float* x = resid32 + row * H;
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = x[i] + to_float(yr[i]) * inv * w[i];
+        x[i] = v;
+        xrow[i] = v;
+        s2 += v * v;
+    }
+    __syncthreads();                                    // scratch is read by all before it is written again
+    s2 = block_sum(s2, scratch);
+    const float inv2 = rsqrtf(s2 / (float)H + eps_next);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) normed[row * H + i] = from_float<T>(xrow[i] * inv2 * w_next[i]);
+}
+
+extern "C" int acorn_rmsnorm_add_norm(float* resid32, const void* y, const float* w, const float* w_next, void* normed,
+                                      int rows, int H, float eps, float eps_next, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if ((size_t)H * sizeof(float) > 48 * 1024) return ACORN_ERR_UNSUPPORTED;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(rmsnorm_add_norm_kernel<T>, dim3(rows), dim3(threads),
+                                                       (size_t)H * sizeof(float), stream, resid32, (const T*)y, w, w_next,
+                                                       (T*)normed, H, eps, eps_next));
     return ACORN_ERR_UNSUPPORTED;
 }
 

@@ -22,7 +22,8 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t ld, T* __
                                    const int* __restrict__ positions, const int* __restrict__ token_row,
                                    const int* __restrict__ block_table, const int* __restrict__ page_base,
                                    int table_stride, T* __restrict__ pages, int H, int dim, int rot, int rank,
-                                   int rot_dims, int P, float eps, int write_kv) {
+                                   int rot_dims, int P, float eps, int write_kv, const T* __restrict__ kv_rows,
+                                   int64_t ld_kv) {
     __shared__ float scratch[32];
     pdl_wait();
     pdl_trigger();
@@ -48,7 +49,8 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t ld, T* __
         qcat[((int64_t)t * H + h) * (rank + rot) + rank + e] = from_float<T>(v);
     }
     if (!write_kv) return;
-    const T* kv = row + (int64_t)H * (dim + rot);
+    // the latent and the shared key part: behind the queries in the same row, or in rows of their own
+    const T* kv = kv_rows ? kv_rows + (int64_t)t * ld_kv : row + (int64_t)H * (dim + rot);
     float ss = 0.f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) {
         const float v = to_float(kv[i]);
@@ -81,13 +83,13 @@ extern "C" int acorn_latent_prep(const void* proj, int64_t ld, void* qcat, const
                                  float mag, const int* positions, const int* token_row, const int* block_table,
                                  const int* page_base, int table_stride, void* pages, int tokens, int H, int dim,
                                  int rot, int rank, int rot_dims, int P, float eps, int write_kv, int dtype,
-                                 cudaStream_t stream) {
+                                 const void* kv_rows, int64_t ld_kv, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (rot_dims % 2 || rot_dims > rot || rot < 0 || rank < 1 || P < 1) return ACORN_ERR_UNSUPPORTED;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(latent_prep_kernel<T>, dim3(tokens), dim3(128), 0, stream,
                                                        (const T*)proj, ld, (T*)qcat, c_weight, inv_freq, mag, positions,
                                                        token_row, block_table, page_base, table_stride, (T*)pages, H,
-                                                       dim, rot, rank, rot_dims, P, eps, write_kv));
+                                                       dim, rot, rank, rot_dims, P, eps, write_kv, (const T*)kv_rows, ld_kv));
     return ACORN_ERR_UNSUPPORTED;
 }
 

@@ -14,7 +14,28 @@
 // layer's cache).  Value heads may have a width of their own (dv; their pages then hold rows of dv),
 // a row of qkv may be wider than its heads (ld elements), and with v_from_k the values are the keys as
 // projected, before norm and rotation: the row then holds no value heads, [q | k] only.
+//
+// Before all that, optionally, a bias per channel and a short causal convolution over time on every
+// channel of q, k and v (conv_w [channels, taps], the last tap for the current token):
+//   u_t = row_t + bias;   x_t = sum_j conv_w[:, j] * u_(t - taps + 1 + j)
+// with the u before a step's first token taken from the request's state slot (the last taps - 1 of
+// them, [taps - 1, channels] float32 in time order, zeros when the request starts; kept up to date by
+// conv_state_update with the same bias).  A token's convolution reads its neighbours' rows as projected,
+// so the queries then go to a buffer of their own (q_out) instead of back into qkv.
 #include "common.cuh"
+
+#define QK_MAX_TAPS 16
+
+struct QkConv {
+    const float* w;           // [channels, taps] or null: no convolution
+    const float* bias;        // [channels] or null
+    const float* state;       // [slots, slot_stride] float32
+    int64_t slot_stride, conv_off;
+    const int* row_start;
+    const int* row_slot;
+    int taps;                 // >= 1 when w is given
+    int channels;             // nq d + nkv d + nkv dv
+};
 
 template <typename T>
 __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__ q_w,
@@ -23,7 +44,8 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
                                   const int* __restrict__ block_table, const int* __restrict__ page_base,
                                   int table_stride, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                   int tokens, int nq, int nkv, int d, int rot, int pairing, int P,
-                                  float eps, int write_kv, int64_t ld, int dv, int v_from_k) {
+                                  float eps, int write_kv, int64_t ld, int dv, int v_from_k, QkConv cv,
+                                  T* __restrict__ q_out, int64_t ld_q) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_trigger();
@@ -38,23 +60,51 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
     T* src = qkv + (int64_t)t * ld + (int64_t)h * d;
     const int pos = positions[t];
 
-    T* dst = src;   // q: in place
+    T* dst = q_out ? q_out + (int64_t)t * ld_q + (int64_t)h * d : src;   // q: in place unless a buffer is given
+    int64_t chan = (int64_t)h * d;                                        // first channel of this head in a row
     if (h >= nq) {
         const int r = token_row[t];
         const int kvh = (h - nq) % nkv;
         const int page = block_table[(int64_t)r * table_stride + (pos / P - page_base[r])];
         const int64_t slot = ((int64_t)page * nkv + kvh) * P + (pos % P);
         dst = (h < nq + nkv) ? k_pages + slot * d : v_pages + slot * dv;
-        if (h >= nq + nkv)      // the value head's source: its own columns, or the key head as projected
-            src = qkv + (int64_t)t * ld + (v_from_k ? (int64_t)(nq + kvh) * d : (int64_t)(nq + nkv) * d + (int64_t)kvh * dv);
+        if (h >= nq + nkv) {    // the value head's source: its own columns, or the key head as projected
+            chan = v_from_k ? (int64_t)(nq + kvh) * d : (int64_t)(nq + nkv) * d + (int64_t)kvh * dv;
+            src = qkv + (int64_t)t * ld + chan;
+        }
     }
+    // element i of this head after bias and convolution (the plain element without them)
+    int i0 = 0;
+    const float* cstate = nullptr;
+    if (cv.w) {
+        const int r = token_row[t];
+        i0 = t - cv.row_start[r];                                         // the token's index within its row
+        if (cv.taps > 1) cstate = cv.state + (int64_t)cv.row_slot[r] * cv.slot_stride + cv.conv_off;
+    }
+    auto element = [&](int i) -> float {
+        const float own = to_float(src[i]) + (cv.bias ? cv.bias[chan + i] : 0.f);
+        if (!cv.w) return own;
+        const float* w = cv.w + (chan + i) * cv.taps;
+        float acc = 0.f;
+        for (int j = 0; j < cv.taps - 1; ++j) {
+            const int idx = i0 - (cv.taps - 1) + j;                       // input index within the row; negative: before the step
+            const float in = idx >= 0 ? to_float(src[(int64_t)(idx - i0) * ld + i]) + (cv.bias ? cv.bias[chan + i] : 0.f)
+                                      : cstate[(int64_t)(cv.taps - 1 + idx) * cv.channels + chan + i];
+            acc = fmaf(w[j], in, acc);
+        }
+        return fmaf(w[cv.taps - 1], own, acc);
+    };
     if (h >= nq + nkv) {   // value head: copy
-        for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+        if (cv.w || cv.bias) {
+            for (int i = lane; i < dv; i += 32) dst[i] = from_float<T>(element(i));
+        } else {
+            for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+        }
         return;
     }
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) {
-        const float v = to_float(src[i]);
+        const float v = element(i);
         x[i] = v;
         ss += v * v;
     }
@@ -192,10 +242,20 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
                                 const int* page_base, int table_stride, void* k_pages, void* v_pages,
                                 int tokens, int nq, int nkv, int d, int rot, int pairing, int P,
                                 float eps, int write_kv, int dtype, int64_t ld, int dv, int v_from_k,
-                                cudaStream_t stream) {
+                                const float* conv_w, int taps, const float* bias, const float* state,
+                                int64_t slot_stride, int64_t conv_off, const int* row_start, const int* row_slot,
+                                void* q_out, int64_t ld_q, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d > 1024 || rot > d || (rot & 1) || dv < 1 || dv > 1024 || (v_from_k && dv != d)) return ACORN_ERR_UNSUPPORTED;
-    if (rot == d && pairing == 0 && dv == d && !v_from_k && ld == (int64_t)(nq + 2 * nkv) * d &&
+    QkConv cv;
+    cv.w = conv_w; cv.bias = bias; cv.state = state; cv.slot_stride = slot_stride; cv.conv_off = conv_off;
+    cv.row_start = row_start; cv.row_slot = row_slot; cv.taps = taps;
+    cv.channels = (nq + nkv) * d + (v_from_k ? 0 : nkv * dv);
+    if (conv_w && (taps < 1 || taps > QK_MAX_TAPS || v_from_k || q_out == nullptr || row_start == nullptr ||
+                   (taps > 1 && (state == nullptr || row_slot == nullptr))))
+        return ACORN_ERR_UNSUPPORTED;
+    const bool plain_rows = conv_w == nullptr && bias == nullptr && q_out == nullptr;
+    if (plain_rows && rot == d && pairing == 0 && dv == d && !v_from_k && ld == (int64_t)(nq + 2 * nkv) * d &&
         (d == 16 || d == 32 || d == 64 || d == 128 || d == 256)) {
 #define ROPE_VEC(G)                                                                                                  \
     ACORN_DISPATCH_DTYPE(dtype, T, return (launch_rope_vec<T, G>((T*)qkv, q_w, k_w, inv_freq, positions, token_row,   \
@@ -219,7 +279,7 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(
         qk_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, (T*)qkv, q_w, k_w, inv_freq,
         positions, token_row, block_table, page_base, table_stride, (T*)k_pages, (T*)v_pages, tokens, nq, nkv, d, rot,
-        pairing, P, eps, write_kv, ld, dv, v_from_k));
+        pairing, P, eps, write_kv, ld, dv, v_from_k, cv, (T*)q_out, ld_q));
     return ACORN_ERR_UNSUPPORTED;
 }
 

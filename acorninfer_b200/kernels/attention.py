@@ -121,14 +121,18 @@ def _key_bound(table_keys: int, window: int | None, chunk: int | None, keep_firs
 
 def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, d: int, scale: float,
                     window: int | None, chunk: int | None = None, keep_first: int = 0,
-                    value_dim: int | None = None) -> torch.Tensor:
+                    value_dim: int | None = None, slopes32: torch.Tensor | None = None,
+                    q: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of all tokens of the step; q is the head of ``qkv`` ([T, >= nq d]).  ``window``, ``chunk``,
     ``keep_first``: which earlier keys a query reads (see ``parts/attention.py``); ``value_dim``: width of the
-    value rows where it is not ``d``.  The tensor-core kernels take values as wide as keys; the TMA decode kernel
-    knows windows only."""
+    value rows where it is not ``d``; ``slopes32`` (float32 [nq]): a penalty ``slope_h * distance to the key`` on
+    the scores; ``q``: the queries where they are not the head of ``qkv`` ([T, >= nq d]).  The tensor-core kernels
+    take values as wide as keys; the TMA decode kernel knows windows only."""
+    if q is not None:
+        qkv = q
     P = cache.k_pages.shape[2]
-    windowed_only = not chunk and not keep_first
-    mask = {"chunk": chunk, "keep_first": keep_first}
+    windowed_only = not chunk and not keep_first and slopes32 is None
+    mask = {"chunk": chunk, "keep_first": keep_first, "slopes32": slopes32}
     if qkv.dtype == torch.bfloat16 and (value_dim is None or value_dim == d):
         if inputs.plan.all_decode and ops.attention_decode_supported(nq, nkv, d) and inputs.num_tokens <= 65535:
             bound = _key_bound(group.block_table.shape[1] * P, window, chunk, keep_first)

@@ -108,16 +108,25 @@ class _Sigs:
     acorn_cast = [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     acorn_qk_rope_kv = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                        c_int, c_int64, c_int, c_int, c_void_p]
+                        c_int, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
+                        c_void_p, c_void_p, c_int64, c_void_p]
     acorn_attention_plain = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                             c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+                             c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
     acorn_bigram_add = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                         c_int, c_int, c_int, c_int, c_void_p]
     acorn_rmsnorm_add = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
+    acorn_rmsnorm_add_norm = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int,
+                              c_void_p]
+    acorn_activation = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_side_gate = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_token_shift = [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_int, c_int, c_int, c_int, c_void_p]
+    acorn_wkv_prep = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_latent_prep = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                         c_int, c_void_p]
+                         c_int, c_void_p, c_int64, c_void_p]
     acorn_latent_attention_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     acorn_latent_attention_tc_supported = [c_int, c_int, c_int, c_int]
@@ -127,10 +136,10 @@ class _Sigs:
                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_conv_state_update = [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
-                               c_int, c_int, c_void_p]
+                               c_int, c_int, c_void_p, c_void_p]
     acorn_delta_rule = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
-                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
-    acorn_delta_out = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
+                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    acorn_delta_out = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
     acorn_moe_route = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_moe_plan = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_grouped_gemm = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
@@ -143,7 +152,7 @@ class _Sigs:
                          c_void_p, c_void_p, c_float, c_void_p]
     acorn_attention_decode = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                              c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+                              c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
     acorn_attention_decode_supported = [c_int, c_int, c_int]
     acorn_attention_decode_tma_main = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                        c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -154,13 +163,13 @@ class _Sigs:
     acorn_attention_decode_merge = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     acorn_attention_prefill = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                               c_int, c_int, c_void_p]
+                               c_int, c_int, c_void_p, c_void_p]
     acorn_attention_prefill_supported = [c_int, c_int, c_int]
     acorn_gemm_tc = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                      c_void_p]
     acorn_attention_prefill_tc = [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                  c_int, c_int, c_int, c_void_p]
+                                  c_int, c_int, c_int, c_void_p, c_void_p]
     acorn_attention_prefill_tc_supported = [c_int, c_int, c_int, c_int]
     acorn_attention_tc_error = []
     acorn_gemm_tc_ex = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
@@ -408,8 +417,12 @@ def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: t
                block_table: torch.Tensor, page_base: torch.Tensor, k_pages: torch.Tensor | None,
                v_pages: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
                rotary_dim: int, interleaved: bool, eps: float, write_kv: bool = True,
-               value_dim: int | None = None, values_from_keys: bool = False) -> None:
-    """Per-head q/k norm, rotary encoding, K/V page write; q is updated in place inside ``qkv``.
+               value_dim: int | None = None, values_from_keys: bool = False, bias32: torch.Tensor | None = None,
+               conv: "ShortConv | None" = None, q_out: torch.Tensor | None = None) -> None:
+    """Per-head q/k norm, rotary encoding, K/V page write; q is updated in place inside ``qkv``, or written
+    to ``q_out`` [T, >= nq d] if that is given.  ``bias32`` (float32, one entry per channel of a row) is added to
+    the row first; ``conv`` then runs a short causal convolution over time on every channel (``q_out`` is needed
+    with it: a token's convolution reads its neighbours' rows as projected).
     ``value_dim``: width of a value head where it is not ``head_dim`` (the value pages then hold rows of
     that width).  ``values_from_keys``: the values are the keys as projected, before norm and rotation; a
     row of ``qkv`` is then ``[q | k]``.  A row may be wider than its heads (further columns are ignored)."""
@@ -442,13 +455,47 @@ def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: t
             raise KernelError(f"cache pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} do not fit "
                               f"nkv={num_kv_heads}, d={head_dim}, dv={dv}")
         P = k_pages.shape[2]
+    channels = (num_heads + num_kv_heads) * head_dim + (0 if values_from_keys else num_kv_heads * dv)
+    if bias32 is not None:
+        _check(bias32, "bias", torch.float32, 1)
+        if bias32.numel() != channels:
+            raise KernelError(f"qk_rope_kv: bias has {bias32.numel()} entries for {channels} channels")
+    if conv is not None:
+        _check(conv.weight32, "conv weight", torch.float32, 2)
+        if conv.weight32.shape[0] != channels or q_out is None or values_from_keys or not write_kv:
+            raise KernelError("qk_rope_kv: the convolution needs a weight row per channel, a query buffer, value "
+                              "columns of their own and a run that writes its cache")
+        if conv.state.shape[1] < conv.offset + (conv.weight32.shape[1] - 1) * channels:
+            raise KernelError("qk_rope_kv: the state slot is too small for the convolution's memory")
+    if q_out is not None:
+        _check(q_out, "q_out", qkv.dtype, 2)
+        if q_out.shape[0] != T or q_out.shape[1] < num_heads * head_dim:
+            raise KernelError(f"qk_rope_kv: q_out {tuple(q_out.shape)} does not hold [{T}, {num_heads * head_dim}]")
     _ok(lib().acorn_qk_rope_kv(qkv.data_ptr(), _ptr(q_weight32), _ptr(k_weight32), inv_freq.data_ptr(),
                                positions.data_ptr(), token_row.data_ptr(), block_table.data_ptr(),
                                page_base.data_ptr(), block_table.stride(0), _ptr(k_pages), _ptr(v_pages), T,
                                num_heads, num_kv_heads, head_dim, rotary_dim, 1 if interleaved else 0,
                                max(P, 1), float(eps), 1 if write_kv else 0, dtype_code(qkv.dtype), qkv.stride(0), dv,
-                               1 if values_from_keys else 0, _stream()),
+                               1 if values_from_keys else 0,
+                               _ptr(conv.weight32) if conv is not None else None,
+                               conv.weight32.shape[1] if conv is not None else 0, _ptr(bias32),
+                               _ptr(conv.state) if conv is not None else None,
+                               conv.state.stride(0) if conv is not None else 0, conv.offset if conv is not None else 0,
+                               _ptr(conv.row_start) if conv is not None else None,
+                               _ptr(conv.row_slot) if conv is not None else None,
+                               _ptr(q_out), q_out.stride(0) if q_out is not None else 0, _stream()),
         "qk_rope_kv")
+
+
+class ShortConv:
+    """What a short causal convolution over time needs of a step: the taps ``weight32`` [channels, taps]
+    (float32, the last tap for the current token), the requests' state slots with the offset at which a
+    slot keeps the last ``taps - 1`` inputs ([taps - 1, channels] float32 in time order), and the step's rows."""
+
+    def __init__(self, weight32: torch.Tensor, state: torch.Tensor, offset: int, row_start: torch.Tensor,
+                 row_slot: torch.Tensor):
+        self.weight32, self.state, self.offset = weight32, state, int(offset)
+        self.row_start, self.row_slot = row_start, row_slot
 
 
 def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -456,13 +503,15 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
                     positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: int | None, out: torch.Tensor | None = None,
                     value_dim: int | None = None, sink32: torch.Tensor | None = None, chunk: int | None = None,
-                    keep_first: int = 0) -> torch.Tensor:
+                    keep_first: int = 0, slopes32: torch.Tensor | None = None) -> torch.Tensor:
     """Paged causal attention for any mix of rows; ``q`` may be the head of a wider buffer
     (row stride ``q_stride`` elements).  Returns [tokens, nq * value_dim].  ``value_dim`` (default
     ``head_dim``): the leading entries of a value row that are summed; ``v_pages`` may be ``k_pages``
     itself.  ``sink32`` (float32 [nq]): a learned term exp(sink) per query head in the softmax denominator.
     ``window`` / ``chunk`` / ``keep_first``: which earlier keys a query reads (the last ``window``
-    positions; those of its own block of ``chunk`` positions; and always the request's first ``keep_first``)."""
+    positions; those of its own block of ``chunk`` positions; and always the request's first ``keep_first``).
+    ``slopes32`` (float32 [nq]): ``slope_h * (query position - key position)`` is taken off every score."""
+    _check_slopes(slopes32, num_heads)
     dv = head_dim if value_dim is None else int(value_dim)
     if not (1 <= dv <= v_pages.shape[3]):
         raise KernelError(f"value_dim must be in 1..{v_pages.shape[3]} (the value rows' width), got {dv}")
@@ -485,9 +534,16 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
                                     block_table.stride(0), token_row.data_ptr(), positions.data_ptr(),
                                     num_tokens, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
                                     float(scale), int(window or 0), dtype_code(q.dtype), dv, _ptr(sink32),
-                                    int(chunk or 0), int(keep_first or 0), v_pages.shape[3], _stream()),
+                                    int(chunk or 0), int(keep_first or 0), v_pages.shape[3], _ptr(slopes32), _stream()),
         "attention_plain")
     return out
+
+
+def _check_slopes(slopes32: torch.Tensor | None, num_heads: int) -> None:
+    if slopes32 is not None:
+        _check(slopes32, "slopes", torch.float32, 1)
+        if slopes32.numel() != num_heads:
+            raise KernelError("slopes must have one entry per query head")
 
 
 def attention_decode_supported(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -503,7 +559,8 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
                      positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
                      scale: float, window: int | None, num_splits: int, token_list: torch.Tensor | None = None,
                      out: torch.Tensor | None = None, scratch: tuple | None = None,
-                     use_tma: bool | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
+                     use_tma: bool | None = None, chunk: int | None = None, keep_first: int = 0,
+                     slopes32: torch.Tensor | None = None) -> torch.Tensor:
     """Split-K decode attention (bfloat16) for single-token rows: the tokens 0..num_tokens-1, or
     those listed in ``token_list``.  ``out`` is [all tokens of the step, nq * d]; rows of tokens
     not handled are left as they are.  ``scratch`` = (part_o float32 [n, nq, splits, d],
@@ -522,7 +579,8 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
     if out is None:
         out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
     P = k_pages.shape[2]
-    if chunk or keep_first:
+    _check_slopes(slopes32, num_heads)
+    if chunk or keep_first or slopes32 is not None:
         if use_tma:
             raise KernelError("attention_decode: the TMA kernel knows windows only")
         use_tma = False
@@ -557,7 +615,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
                                      token_row.data_ptr(), positions.data_ptr(), _ptr(token_list), n, num_heads,
                                      num_kv_heads, head_dim, P, float(scale), int(window or 0),
                                      num_splits, _ptr(part_o), _ptr(part_lse), int(chunk or 0), int(keep_first or 0),
-                                     _stream()), "attention_decode")
+                                     _ptr(slopes32), _stream()), "attention_decode")
     return out
 
 
@@ -569,9 +627,11 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_p
                       block_table: torch.Tensor, page_base: torch.Tensor, row_start: torch.Tensor,
                       row_pos: torch.Tensor, tiles: torch.Tensor, num_tokens: int, num_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: int | None,
-                      out: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
+                      out: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0,
+                      slopes32: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core prefill attention (bfloat16) for the query tiles listed in ``tiles``
     (int32 [n, 2]: row, first token within the row; 64 tokens a tile at most)."""
+    _check_slopes(slopes32, num_heads)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill takes bfloat16")
     if not attention_prefill_supported(num_heads, num_kv_heads, head_dim):
@@ -586,7 +646,7 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_p
                                       block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
                                       row_start.data_ptr(), row_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0],
                                       num_heads, num_kv_heads, head_dim, k_pages.shape[2], float(scale),
-                                      int(window or 0), int(chunk or 0), int(keep_first or 0), _stream()),
+                                      int(window or 0), int(chunk or 0), int(keep_first or 0), _ptr(slopes32), _stream()),
         "attention_prefill")
     return out
 
@@ -599,12 +659,16 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, 
                          block_table: torch.Tensor, page_base: torch.Tensor, row_start: torch.Tensor,
                          row_pos: torch.Tensor, tiles: torch.Tensor, num_tokens: int, num_heads: int,
                          num_kv_heads: int, head_dim: int, scale: float, window: int | None,
-                         out: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0) -> torch.Tensor:
+                         out: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0,
+                         slopes32: torch.Tensor | None = None) -> torch.Tensor:
     """tcgen05/TMA prefill attention (bfloat16, head size 128) for the query tiles listed in
     ``tiles`` (int32 [n, 2]: row, first token within the row; 128 tokens a tile at most).  CTAs
     start in the order of the list: give the tiles that read the most keys first."""
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc takes bfloat16")
+    _check_slopes(slopes32, num_heads)
+    if slopes32 is not None and not scale > 0:
+        raise KernelError("attention_prefill_tc: slopes need a positive scale")
     _check(k_pages, "k_pages", q.dtype, 4)
     _check(v_pages, "v_pages", q.dtype, 4)
     if not attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim, k_pages.shape[2]):
@@ -621,7 +685,8 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, 
                                          page_base.data_ptr(), block_table.stride(0), row_start.data_ptr(),
                                          row_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], num_heads,
                                          num_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window or 0),
-                                         int(chunk or 0), int(keep_first or 0), _stream()), "attention_prefill_tc")
+                                         int(chunk or 0), int(keep_first or 0), _ptr(slopes32), _stream()),
+        "attention_prefill_tc")
     return out
 
 
@@ -1070,21 +1135,48 @@ def rmsnorm_add(resid32: torch.Tensor, y: torch.Tensor, weight32: torch.Tensor, 
     return out
 
 
+def rmsnorm_add_norm(resid32: torch.Tensor, y: torch.Tensor, weight32: torch.Tensor, eps: float,
+                     next_weight32: torch.Tensor, next_eps: float) -> torch.Tensor:
+    """resid32 += rmsnorm(y) * weight (in place, float32), then the RMS norm of the new rows with
+    ``next_weight32``, in ``y``'s dtype: a sublayer's output norm and the next sublayer's input norm at once."""
+    _check(resid32, "resid32", torch.float32, 2)
+    _check(y, "y", None, 2)
+    _check(weight32, "weight", torch.float32, 1)
+    _check(next_weight32, "next weight", torch.float32, 1)
+    H = y.shape[1]
+    if y.shape != resid32.shape or weight32.numel() != H or next_weight32.numel() != H:
+        raise KernelError(f"rmsnorm_add_norm: y {tuple(y.shape)}, residual {tuple(resid32.shape)}, weights "
+                          f"{weight32.numel()} / {next_weight32.numel()}")
+    out = torch.empty_like(y)
+    _ok(lib().acorn_rmsnorm_add_norm(resid32.data_ptr(), y.data_ptr(), weight32.data_ptr(), next_weight32.data_ptr(),
+                                     out.data_ptr(), y.shape[0], H, float(eps), float(next_eps), dtype_code(y.dtype),
+                                     _stream()), "rmsnorm_add_norm")
+    return out
+
+
+RMSNORM_ADD_NORM_MAX_WIDTH = 12288          # the updated row waits in shared memory (48 KB of float32)
+
+
 # ------------------------------------------------------------------ attention through a latent
 
 
 def latent_prep(proj: torch.Tensor, qcat: torch.Tensor, c_weight32: torch.Tensor | None, inv_freq: torch.Tensor,
                 magnitude: float, positions: torch.Tensor, token_row: torch.Tensor, block_table: torch.Tensor,
                 page_base: torch.Tensor, pages: torch.Tensor | None, num_heads: int, dim: int, rot: int, rank: int,
-                rot_dims: int, eps: float) -> None:
+                rot_dims: int, eps: float, kv_rows: torch.Tensor | None = None) -> None:
     """Rotates the rotated part of every head's query into ``qcat[t, h, rank:]`` and, with ``pages``
     ([pages, 1, P, rank + rot]), writes the token's cache row: the RMS-normed latent and the rotated
-    shared key part.  ``proj`` [T, H (dim + rot) (+ rank + rot)]."""
+    shared key part.  ``proj`` [T, H (dim + rot) (+ rank + rot)]; with ``kv_rows`` [T, rank + rot] the latent and
+    the shared key part are read from there and ``proj`` holds the queries only."""
     _check(proj, "proj", None, 2)
     _check(qcat, "qcat", proj.dtype, 3)
     T = proj.shape[0]
     write = pages is not None
-    want = num_heads * (dim + rot) + (rank + rot if write else 0)
+    want = num_heads * (dim + rot) + (rank + rot if write and kv_rows is None else 0)
+    if kv_rows is not None:
+        _check(kv_rows, "kv_rows", proj.dtype, 2)
+        if kv_rows.shape != (T, rank + rot) or kv_rows.stride(1) != 1:
+            raise KernelError(f"latent_prep: kv_rows {tuple(kv_rows.shape)} is not [T, rank + rot]")
     if proj.shape[1] != want or qcat.shape != (T, num_heads, rank + rot):
         raise KernelError(f"latent_prep: proj {tuple(proj.shape)} / qcat {tuple(qcat.shape)} do not fit H={num_heads}, "
                           f"dim={dim}, rot={rot}, rank={rank}")
@@ -1101,7 +1193,8 @@ def latent_prep(proj: torch.Tensor, qcat: torch.Tensor, c_weight32: torch.Tensor
     _ok(lib().acorn_latent_prep(proj.data_ptr(), proj.stride(0), qcat.data_ptr(), _ptr(c_weight32), inv_freq.data_ptr(),
                                 float(magnitude), positions.data_ptr(), token_row.data_ptr(), block_table.data_ptr(),
                                 page_base.data_ptr(), block_table.stride(0), _ptr(pages), T, num_heads, dim, rot, rank,
-                                rot_dims, P, float(eps), 1 if write else 0, dtype_code(proj.dtype), _stream()), "latent_prep")
+                                rot_dims, P, float(eps), 1 if write else 0, dtype_code(proj.dtype), _ptr(kv_rows),
+                                kv_rows.stride(0) if kv_rows is not None else 0, _stream()), "latent_prep")
 
 
 LATENT_TILE_ROWS = 64          # (token, head) pairs a block of the tensor-core kernel takes
@@ -1196,42 +1289,137 @@ def delta_prep(main: torch.Tensor, up32: torch.Tensor, conv_w32: torch.Tensor, s
 
 
 def conv_state_update(main: torch.Tensor, state: torch.Tensor, conv_off: int, row_start: torch.Tensor,
-                      row_slot: torch.Tensor, num_rows: int, channels: int, taps: int, skip_single: bool = False) -> None:
+                      row_slot: torch.Tensor, num_rows: int, channels: int, taps: int, skip_single: bool = False,
+                      bias32: torch.Tensor | None = None) -> None:
     """The last ``taps - 1`` convolution inputs of every row's request into its state.  ``skip_single``: rows of
-    one token are left alone (the kernel before has shifted their memory: ``ssm_prep(update_single=True)``)."""
+    one token are left alone (the kernel before has shifted their memory: ``ssm_prep(update_single=True)``).
+    ``bias32`` (float32 [channels]): added to the inputs as they are kept."""
+    if bias32 is not None:
+        _check(bias32, "bias", torch.float32, 1)
+        if bias32.numel() != channels:
+            raise KernelError("conv_state_update: one bias entry per channel")
+    if main.shape[1] < channels or state.shape[1] < conv_off + (taps - 1) * channels:
+        raise KernelError("conv_state_update: rows or state slots too small for the channels")
     _ok(lib().acorn_conv_state_update(main.data_ptr(), main.stride(0), state.data_ptr(), state.stride(0), int(conv_off),
                                       row_start.data_ptr(), row_slot.data_ptr(), num_rows, channels, taps,
-                                      dtype_code(main.dtype), 1 if skip_single else 0, _stream()), "conv_state_update")
+                                      dtype_code(main.dtype), 1 if skip_single else 0, _ptr(bias32), _stream()),
+        "conv_state_update")
 
 
-def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, g: torch.Tensor,
-               state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor, num_rows: int) -> torch.Tensor:
+def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor | None, g: torch.Tensor,
+               state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor, num_rows: int,
+               bonus32: torch.Tensor | None = None) -> torch.Tensor:
     """The recurrence over every row's tokens from the state in its slot (updated in place): float32
-    o [T, H, vdim]."""
+    o [T, H, vdim].  With ``bonus32`` (float32 [H, dim]) and no ``beta`` the form without the delta correction
+    whose output reads the state before the token's decay and write and sees the token itself through the
+    bonus: ``o = S^T q + (sum_d q_d bonus_d k_d) v;  S = diag(g) S + k v^T``."""
     T, H, vdim = v.shape
     KH, dim = q.shape[1], q.shape[2]
-    for t, n in ((q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (g, "g")):
+    if (beta is None) == (bonus32 is None):
+        raise KernelError("delta_rule: give beta (the delta rule) or bonus32 (the form that reads the state first)")
+    if bonus32 is not None:
+        _check(bonus32, "bonus", torch.float32, 2)
+        if bonus32.shape != (H, dim):
+            raise KernelError(f"delta_rule: bonus {tuple(bonus32.shape)} is not [H, dim] = [{H}, {dim}]")
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (g, "g")) + (((beta, "beta"),) if beta is not None else ()):
         _check(t, n, torch.float32)
     _check(state, "state", torch.float32, 2)
     if state.shape[1] < H * dim * vdim or g.shape != (T, H, dim) or dim > 256:
         raise KernelError(f"delta_rule: sizes do not fit (state {tuple(state.shape)}, H={H}, dim={dim}, vdim={vdim})")
     out = torch.empty((T, H, vdim), dtype=torch.float32, device=v.device)
-    _ok(lib().acorn_delta_rule(q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), g.data_ptr(), state.data_ptr(),
+    _ok(lib().acorn_delta_rule(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(beta), g.data_ptr(), state.data_ptr(),
                                state.stride(0), row_start.data_ptr(), row_slot.data_ptr(), out.data_ptr(), num_rows, H, KH,
-                               dim, vdim, _stream()), "delta_rule")
+                               dim, vdim, _ptr(bonus32), _stream()), "delta_rule")
     return out
 
 
 def delta_out(o32: torch.Tensor, gate32: torch.Tensor, weight32: torch.Tensor, eps: float, dtype: torch.dtype) -> torch.Tensor:
-    """Per token and head o / rms(o) * weight * gate -> [T, H * vdim] in ``dtype``."""
+    """Per token and head o / rms(o) * weight * gate -> [T, H * vdim] in ``dtype``.  ``weight32``: [vdim],
+    shared by the heads, or [H * vdim], a weight per head."""
     T, H, vdim = o32.shape
     _check(o32, "o", torch.float32, 3)
     _check(gate32, "gate", torch.float32, 3)
     _check(weight32, "weight", torch.float32, 1)
+    if weight32.numel() not in (vdim, H * vdim):
+        raise KernelError(f"delta_out: weight of {weight32.numel()} entries for heads of {vdim} ({H} heads)")
     y = torch.empty((T, H * vdim), dtype=dtype, device=o32.device)
     _ok(lib().acorn_delta_out(o32.data_ptr(), gate32.data_ptr(), weight32.data_ptr(), y.data_ptr(), T, H, vdim, float(eps),
-                              dtype_code(dtype), _stream()), "delta_out")
+                              dtype_code(dtype), 1 if (weight32.numel() == H * vdim and H > 1) else 0, _stream()), "delta_out")
     return y
+
+
+# ------------------------------------------------------------------ time mixing with a matrix state
+
+
+def token_shift(h: torch.Tensor, mu32: torch.Tensor, state: torch.Tensor, prev_off: int, token_row: torch.Tensor,
+                row_start: torch.Tensor, row_slot: torch.Tensor) -> torch.Tensor:
+    """``out[s, t] = h[t] + (prev[t] - h[t]) * mu32[s]`` for every blend s: ``prev`` is the row before ``t`` in its
+    request, for a step's first token the float32 row kept in the request's state slot at ``prev_off`` (which
+    ``conv_state_update`` with two taps keeps).  h [T, W]; mu32 [n, W]; returns [n, T, W] in h's dtype."""
+    _check(h, "h", None, 2)
+    _check(mu32, "mu", torch.float32, 2)
+    _check(state, "state", torch.float32, 2)
+    T, W = h.shape
+    n = mu32.shape[0]
+    if mu32.shape[1] != W or not mu32.is_contiguous() or state.shape[1] < prev_off + W or h.stride(1) != 1:
+        raise KernelError(f"token_shift: h {tuple(h.shape)}, mu {tuple(mu32.shape)}, state {tuple(state.shape)} do not fit")
+    out = torch.empty((n, T, W), dtype=h.dtype, device=h.device)
+    _ok(lib().acorn_token_shift(h.data_ptr(), h.stride(0), mu32.data_ptr(), state.data_ptr(), state.stride(0), int(prev_off),
+                                token_row.data_ptr(), row_start.data_ptr(), row_slot.data_ptr(), out.data_ptr(), T, W, n,
+                                dtype_code(h.dtype), _stream()), "token_shift")
+    return out
+
+
+def wkv_prep(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, z32: torch.Tensor, w0_32: torch.Tensor,
+             heads: int):
+    """For the recurrence, float32 [T, H, dim] each: r, k, v as they are, the decay ``exp(-exp(z + w0))`` and the
+    gate ``silu(g)``.  r, k, v, g: [T, H dim] of the activation dtype with one row stride; z32 [T, H dim] float32."""
+    T, C = r.shape
+    for t, n in ((r, "r"), (k, "k"), (v, "v"), (g, "g")):
+        _check(t, n, r.dtype, 2)
+        if t.shape != (T, C) or t.stride(0) != r.stride(0) or t.stride(1) != 1:
+            raise KernelError("wkv_prep: r, k, v, g must have one shape and row stride")
+    _check(z32, "z", torch.float32, 2)
+    _check(w0_32, "w0", torch.float32, 1)
+    if z32.shape != (T, C) or w0_32.numel() != C or C % heads:
+        raise KernelError(f"wkv_prep: z {tuple(z32.shape)} / w0 {w0_32.numel()} do not fit [{T}, {C}]")
+    outs = torch.empty((5, T, heads, C // heads), dtype=torch.float32, device=r.device)
+    _ok(lib().acorn_wkv_prep(r.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), r.stride(0), z32.data_ptr(),
+                             z32.stride(0), w0_32.data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(),
+                             outs[3].data_ptr(), outs[4].data_ptr(), T, C, dtype_code(r.dtype), _stream()), "wkv_prep")
+    return outs[0], outs[1], outs[2], outs[3], outs[4]
+
+
+# ------------------------------------------------------------------ plain activations, a token's side rows
+
+ACTIVATIONS = {"relu_squared": 0, "tanh": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """``act(x)`` elementwise over rows [T, n] (a row stride is allowed); float32 arithmetic, one rounding."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation must be one of {sorted(ACTIVATIONS)}, got {kind!r}")
+    _check(x, "x", None, 2)
+    if x.stride(1) != 1:
+        raise KernelError("activation: rows must be contiguous")
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    _ok(lib().acorn_activation(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], ACTIVATIONS[kind],
+                               dtype_code(x.dtype), _stream()), "activation")
+    return out
+
+
+def side_gate(z: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, col0: int) -> torch.Tensor:
+    """``gelu_tanh(z[t]) * table[token_ids[t], col0 : col0 + n]`` for z [T, n]."""
+    _check(z, "z", None, 2)
+    _check(table, "table", z.dtype, 2)
+    _check(token_ids, "token_ids", torch.int32, 1)
+    T, n = z.shape
+    if not z.is_contiguous() or table.stride(1) != 1 or col0 < 0 or col0 + n > table.shape[1]:
+        raise KernelError(f"side_gate: z {tuple(z.shape)} / table {tuple(table.shape)} / first column {col0} do not fit")
+    out = torch.empty_like(z)
+    _ok(lib().acorn_side_gate(z.data_ptr(), token_ids.data_ptr(), table.data_ptr(), table.stride(0), int(col0),
+                              out.data_ptr(), T, n, dtype_code(z.dtype), _stream()), "side_gate")
+    return out
 
 
 # ------------------------------------------------------------------ layer norm, sums, head gates

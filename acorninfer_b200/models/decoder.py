@@ -17,7 +17,7 @@ import torch
 
 from .. import parts as _parts  # noqa: F401  (registers the built-in part kinds)
 from ..kernels import ops
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, STAGES, BuildContext, KVNeeds,
+from ..parts.base import (BLOCKS, FEED_FORWARDS, LAYER_EXTRAS, MIXERS, NORMS, POSITION_ENCODINGS, STAGES, BuildContext, KVNeeds,
                           ModelSpec, StateNeeds, TensorSpec, build_part)
 
 
@@ -48,14 +48,17 @@ class Decoder:
             mixer = build_part(MIXERS, ls.mixer, self.ctx)
             ff = build_part(FEED_FORWARDS, ls.feed_forward, self.ctx) if ls.feed_forward is not None else None
             norms = {k: build_part(NORMS, v, self.ctx) for k, v in ls.norms.items()}
+            extras = {k: build_part(LAYER_EXTRAS, v, self.ctx) for k, v in ls.extras.items()}
             block = BLOCKS.get(ls.block.kind)(ctx=self.ctx, mixer=mixer, feed_forward=ff, norms=norms,
-                                              **ls.block.params)
+                                              **({"extras": extras} if extras else {}), **ls.block.params)
             self.blocks.append(block)
             self._named_parts.append((ls.mixer.prefix, mixer))
             if ff is not None:
                 self._named_parts.append((ls.feed_forward.prefix, ff))
             for k, v in ls.norms.items():
                 self._named_parts.append((v.prefix, norms[k]))
+            for k, v in ls.extras.items():
+                self._named_parts.append((v.prefix, extras[k]))
             self._named_parts.append((ls.block.prefix, block))
         self.final_norm = build_part(NORMS, spec.final_norm, self.ctx)
         self._named_parts.append((spec.final_norm.prefix, self.final_norm))
@@ -165,10 +168,23 @@ class Decoder:
             resid32 = stage.forward(resid32, inputs)
         delta = None
         sched = self.spec.schedule
+        # a run that takes the tokens in again adds the stream as it was here
+        entered32 = resid32.clone() if any(e.add_embedding for e in sched) else None
         for i, e in enumerate(sched):
+            if e.add_embedding:
+                if isinstance(delta, ops.NormedRows):
+                    raise ValueError(f"schedule entry {i} adds the token rows, but the run before it already "
+                                     "prepared this run's first norm")
+                if isinstance(delta, ops.DeltaPair):
+                    delta = ops.fold_pair(resid32, delta)
+                if delta is not None and not isinstance(delta, ops.RoundedRows):
+                    ops.add_into(resid32, delta)
+                delta = None
+                ops.add_into(resid32, entered32)
             # the norm that consumes this run's output: the next run's first norm (the final norm
             # works on selected rows only and keeps its own kernel)
-            nxt = self.blocks[sched[i + 1].layer].first_norm(inputs.num_tokens) if i + 1 < len(sched) else None
+            nxt = self.blocks[sched[i + 1].layer].first_norm(inputs.num_tokens) \
+                if i + 1 < len(sched) and not sched[i + 1].add_embedding else None
             resid32, delta = self.blocks[e.layer].forward(resid32, delta, inputs, caches[i], next_norm=nxt)
             # two pending results (a block whose sublayers run side by side): whoever comes next adds both, or
             # the first is added here

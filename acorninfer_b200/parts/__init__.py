@@ -1,7 +1,7 @@
 """Parts that layers are put together from.  Importing the package registers the built-in kinds."""
 
 from . import (attention, bigram, block, channel_delta, feed_forward, latent_attention, linear_recurrence,  # noqa: F401
-               norms, rope, routed_experts, side_by_side)
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, BuildContext,  # noqa: F401
-                   CacheNeeds, FeedForward, KVNeeds, LayerSpec, Mixer, ModelSpec, Norm, Part, PartSpec,
+               norms, rope, routed_experts, side_by_side, time_mix, token_side)
+from .base import (BLOCKS, FEED_FORWARDS, LAYER_EXTRAS, MIXERS, NORMS, POSITION_ENCODINGS, Block, BuildContext,  # noqa: F401
+                   CacheNeeds, FeedForward, KVNeeds, LayerExtra, LayerSpec, Mixer, ModelSpec, Norm, Part, PartSpec,
                    PositionEncoding, ScheduleEntry, Stage, StateNeeds, TensorSpec)

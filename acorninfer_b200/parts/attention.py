@@ -13,7 +13,12 @@ block of ``chunk`` positions (blocks counted from position 0 of the request); an
 rule, the request's first ``keep_first`` keys.  Options: value heads of a width of their own
 (``value_dim``); values that are the keys as projected, before norm and rotation
 (``values_from_keys``: no value matrix); a gate per head on the heads' outputs,
-``sigmoid(W_g x)_h``, a function of the mixer's input (``head_gate``).
+``sigmoid(W_g x)_h``, a function of the mixer's input (``head_gate``); biases on the q, k, v projections
+(``bias``); a short causal convolution over time on every channel of q, k and v, directly after the
+projection and before the norm (``conv_taps``; the last ``conv_taps - 1`` projected rows of a request
+are its state, float32, in its state slot); a penalty on the distance to the key,
+``score = q . k * scale - slope_h * (i - j)`` with ``slope_h = 2^(-slope_exponent * (h + 1) / heads)``
+(``slope_exponent``).
 
 All sizes are parameters.  The q, k, v (and gate) matrices are concatenated when bound so that one
 matrix product yields a token's whole row.  A run that reads another run's
@@ -26,10 +31,12 @@ import torch
 
 from ..kernels import ops
 from ..kernels import attention as attn_kernels
-from .base import MIXERS, BuildContext, CacheNeeds, KVNeeds, Mixer, TensorSpec
+from .base import MIXERS, BuildContext, CacheNeeds, KVNeeds, Mixer, StateNeeds, TensorSpec
 
 _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-          "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "gate": "g_proj.weight"}
+          "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "gate": "g_proj.weight",
+          "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+          "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight"}
 
 
 @MIXERS.register("attention")
@@ -42,8 +49,12 @@ class Attention(Mixer):
                  position: str | None, scale: float, qk_norm_eps: float | None = None,
                  window: int | None = None, chunk: int | None = None, keep_first: int = 0,
                  value_dim: int | None = None, values_from_keys: bool = False, head_gate: bool = False,
-                 names: dict | None = None):
-        """``names``: the tensors' names relative to the part's prefix (keys q, k, v, o, q_norm, k_norm, gate)."""
+                 names: dict | None = None, bias: bool = False, conv_taps: int | None = None,
+                 slope_exponent: float | None = None):
+        """``names``: the tensors' names relative to the part's prefix (keys q, k, v, o, q_norm, k_norm, gate,
+        q_bias, k_bias, v_bias, q_conv, k_conv, v_conv)."""
+        if conv_taps is not None and (conv_taps < 1 or values_from_keys):
+            raise ValueError("conv_taps must be >= 1 or None, and needs value columns of their own")
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads ({num_heads}) must be a multiple of num_kv_heads ({num_kv_heads})")
         for what, n in (("window", window), ("chunk", chunk)):
@@ -66,7 +77,14 @@ class Attention(Mixer):
         if self.position is not None and self.position.head_dim != head_dim:
             raise ValueError("position encoding was built for another head size")
         # the plain arrangement [q | k | v] of equal head sizes, which the fused products take
-        self.plain = not (values_from_keys or head_gate) and self.dv == head_dim
+        self.bias, self.taps = bool(bias), conv_taps
+        self.slopes32 = None
+        if slope_exponent is not None:
+            self.slopes32 = torch.tensor([2.0 ** (-float(slope_exponent) * (h + 1) / num_heads) for h in range(num_heads)],
+                                         dtype=torch.float64).to(torch.float32)
+        self.channels = (num_heads + num_kv_heads) * head_dim + (0 if values_from_keys else num_kv_heads * self.dv)
+        self.bias32 = self.conv32 = None
+        self.plain = not (values_from_keys or head_gate or bias or conv_taps) and self.dv == head_dim
         self.gate_col = (self.nq + self.nkv) * self.d + (0 if values_from_keys else self.nkv * self.dv)
         self.w_qkv = self.w_o = self.q_norm32 = self.k_norm32 = None
 
@@ -84,6 +102,12 @@ class Attention(Mixer):
         if self.qk_norm_eps is not None:
             specs[n["q_norm"]] = TensorSpec((self.d,), "norm")
             specs[n["k_norm"]] = TensorSpec((self.d,), "norm")
+        rows = {"q": self.nq * self.d, "k": self.nkv * self.d, **({} if self.values_from_keys else {"v": self.nkv * self.dv})}
+        for which, size in rows.items():
+            if self.bias:
+                specs[n[which + "_bias"]] = TensorSpec((size,), "bias")
+            if self.taps:
+                specs[n[which + "_conv"]] = TensorSpec((size, self.taps), "conv")
         return specs
 
     def bind(self, tensors):
@@ -102,10 +126,20 @@ class Attention(Mixer):
         if self.qk_norm_eps is not None:
             self.q_norm32 = tensors[n["q_norm"]].to(torch.float32).contiguous()
             self.k_norm32 = tensors[n["k_norm"]].to(torch.float32).contiguous()
+        which = ("q", "k") + (() if self.values_from_keys else ("v",))
+        if self.bias:
+            self.bias32 = torch.cat([tensors[n[w + "_bias"]].to(torch.float32) for w in which]).contiguous()
+        if self.taps:
+            self.conv32 = torch.cat([tensors[n[w + "_conv"]].to(torch.float32) for w in which], dim=0).contiguous()
+        if self.slopes32 is not None:
+            self.slopes32 = self.slopes32.to(self.w_o.device)
 
     def cache_needs(self):
-        return CacheNeeds(kv=KVNeeds(self.nkv, self.d, self.window, chunk=self.chunk, keep_first=self.keep_first,
-                                     value_dim=None if self.dv == self.d else self.dv))
+        kv = KVNeeds(self.nkv, self.d, self.window, chunk=self.chunk, keep_first=self.keep_first,
+                     value_dim=None if self.dv == self.d else self.dv)
+        # the convolutions' memory: the last taps - 1 rows as projected (with their biases), float32
+        state = StateNeeds(((self.taps - 1) * self.channels,)) if self.taps and self.taps > 1 and self.channels else None
+        return CacheNeeds(kv=kv, state=state)
 
     def step_arrays(self):
         return attn_kernels.STEP_ARRAYS
@@ -124,6 +158,7 @@ class Attention(Mixer):
         g = inputs.groups[cache.group]
         pos = self.position
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
+        proj = None                 # the projected rows where the queries do not stay among them
         if (self.plain and pos is not None and self.w_qkv.dtype == torch.bfloat16 and ops.gemm_tc_supported(
                 x.x if isinstance(x, ops.NormedRows) else x, self.w_qkv)
                 and self._rows_fuse(rows)
@@ -135,6 +170,25 @@ class Attention(Mixer):
                 self.q_norm32, self.k_norm32, pos.inv_freq, self.nq, self.nkv,
                 self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
                 cos_sin=pos.table(inputs) if rows > ops.GEMM_TC_MAX_ROWS and hasattr(pos, "table") else None))
+        elif self.bias or self.taps:
+            if not cache.write:
+                raise ValueError("attention: biased or convolved projections need a cache of the run's own")
+            proj = ops.linear(x, self.w_qkv, out_dtype=self.ctx.dtype)
+            qkv = torch.empty((rows, self.nq * self.d), dtype=self.ctx.dtype, device=proj.device)      # the queries
+            conv = None
+            if self.taps:
+                conv = ops.ShortConv(self.conv32, cache.state if self.taps > 1 else proj.new_zeros((1, 0), dtype=torch.float32),
+                                     0, inputs.row_start, inputs.row_slot)
+            ops.qk_rope_kv(proj, self.q_norm32, self.k_norm32,
+                           pos.inv_freq if pos is not None else _no_freq(self.ctx.device),
+                           inputs.positions, inputs.token_row, g.block_table, g.page_base,
+                           cache.k_pages, cache.v_pages, self.nq, self.nkv, self.d,
+                           pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
+                           self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=True,
+                           value_dim=self.dv, bias32=self.bias32, conv=conv, q_out=qkv)
+            if self.taps and self.taps > 1:
+                ops.conv_state_update(proj, cache.state, 0, inputs.row_start, inputs.row_slot, inputs.num_rows,
+                                      self.channels, self.taps, bias32=self.bias32)
         else:
             qkv = ops.linear(x, self.w_qkv, out_dtype=self.ctx.dtype)
             ops.qk_rope_kv(qkv, self.q_norm32, self.k_norm32,
@@ -145,9 +199,11 @@ class Attention(Mixer):
                            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.write,
                            value_dim=self.dv, values_from_keys=self.values_from_keys)
         heads = attn_kernels.paged_attention(qkv, inputs, g, cache, self.nq, self.nkv, self.d, self.scale, self.window,
-                                             chunk=self.chunk, keep_first=self.keep_first, value_dim=self.dv)
+                                             chunk=self.chunk, keep_first=self.keep_first, value_dim=self.dv,
+                                             slopes32=self.slopes32)
         if self.head_gate or out_scale != 1.0 or out is not None:
-            return ops.head_gate(heads, qkv[:, self.gate_col:] if self.head_gate else None, self.nq, out_scale, out=out)
+            gate_rows = qkv if proj is None else proj
+            return ops.head_gate(heads, gate_rows[:, self.gate_col:] if self.head_gate else None, self.nq, out_scale, out=out)
         return heads
 
     def forward(self, x, inputs, cache, epilogue=None, residual32=None):

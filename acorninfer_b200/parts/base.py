@@ -15,6 +15,7 @@ Interfaces
 ``FeedForward``       ``forward(x, inputs) -> delta``
 ``Block``             ``forward(resid32, delta, inputs, cache) -> (resid32, delta)``
 ``Stage``             ``forward(x, inputs) -> x`` outside the layers (after the token table, around the head)
+``LayerExtra``        ``forward(resid32, rows, inputs)``: a further sublayer that adds to the stream itself
 
 All activations are ``[tokens, width]`` over the flat token dimension of one step.
 The residual stream is kept in float32 (``resid32``); what a part adds to it
@@ -58,22 +59,28 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: the arrangement (``block``) and the parts it arranges.  ``feed_forward`` None: a
-    layer of a mixer alone (the arrangement must allow it)."""
+    layer of a mixer alone (the arrangement must allow it).  ``extras``: further sublayers by the name under
+    which the arrangement knows them (kinds of the ``LAYER_EXTRAS`` registry); arrangements that know none
+    refuse them."""
 
     block: PartSpec
     mixer: PartSpec
     feed_forward: PartSpec | None
     norms: dict[str, PartSpec]
+    extras: dict[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  ``layer`` indexes ``ModelSpec.layers`` and may appear in
     several entries.  ``reads_cache_of`` names an earlier entry whose cache this run
-    reads instead of writing one of its own."""
+    reads instead of writing one of its own.  ``add_embedding``: the stream as it entered the first layer
+    (the token rows after the stages that follow the token table) is added to the stream before this run:
+    a span of layers that runs several times in a row takes the tokens in again at each pass."""
 
     layer: int
     reads_cache_of: int | None = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -259,6 +266,15 @@ class Stage(Part):
         raise NotImplementedError
 
 
+class LayerExtra(Part):
+    """A further sublayer of a layer beside its mixer and feed-forward, placed by the arrangement that names
+    it.  ``forward(resid32, rows, inputs)`` adds its result to the float32 stream in place; ``rows`` is the
+    stream as a sublayer reads it (rounded to the activation dtype; the stream itself under a float32 engine)."""
+
+    def forward(self, resid32: torch.Tensor, rows: torch.Tensor, inputs: "Any") -> None:
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arrangement of a mixer, a feed-forward and norms around the residual stream."""
 
@@ -322,6 +338,7 @@ NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
 STAGES = Registry("model stage")
+LAYER_EXTRAS = Registry("layer extra")
 
 
 def build_part(registry: Registry, spec: PartSpec, ctx: BuildContext, **extra):

@@ -13,6 +13,12 @@ is what the next sublayer reads (``RoundedRows``).  A layer may have no feed-for
 ``parallel``: ``h = norm(x); x += mixer(h) + feed_forward(h)``: one norm, both sublayers read its
 output.  Both results are added in float32: by the product that made them where it can add into the
 stream itself, else by the norm kernel of the next block (``DeltaPair``).  A layer may have no feed-forward.
+
+``sandwich``: ``x += norm_mo(mixer(norm_mi(x))); x += norm_fo(feed_forward(norm_fi(x)))``: a norm before and
+after every sublayer (norms ``mixer_in``, ``mixer_out``, ``feed_forward_in``, ``feed_forward_out``), the sums in
+float32 in the kernel that norms a sublayer's output, which where it can also applies the norm the next
+sublayer reads the stream through.  A layer may have no feed-forward; an extra named ``side`` (a sublayer that
+adds to the stream itself, such as a token's side rows) runs last.
 """
 
 from __future__ import annotations
@@ -129,3 +135,47 @@ class ParallelBlock(Block):
         if a is None or b is None:
             return resid32, (a if b is None else b)
         return resid32, ops.DeltaPair(a, b)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    graph_safe = True
+
+    def __init__(self, ctx, mixer, feed_forward, norms, extras=None):
+        super().__init__(mixer, feed_forward, norms)
+        self.ctx = ctx
+        want = {"mixer_in", "mixer_out"} | ({"feed_forward_in", "feed_forward_out"} if feed_forward is not None else set())
+        if want - set(norms):
+            raise ValueError(f"sandwich block needs norms named {sorted(want)}; missing {sorted(want - set(norms))}")
+        extras = extras or {}
+        if set(extras) - {"side"}:
+            raise ValueError(f"sandwich block knows the extra 'side' only, got {sorted(extras)}")
+        self.side = extras.get("side")
+
+    @staticmethod
+    def _pair_fuses(out_norm, in_norm, width):
+        return (hasattr(out_norm, "normed_add_norm") and hasattr(in_norm, "weight32")
+                and width <= ops.RMSNORM_ADD_NORM_MAX_WIDTH)
+
+    def forward(self, resid32, delta, inputs, cache, next_norm=None):
+        if isinstance(delta, ops.NormedRows):
+            raise ValueError("a sandwich block cannot follow a block that fused the next norm into its last product")
+        if isinstance(delta, ops.RoundedRows):          # the block before added its result itself
+            delta = None
+        n = self.norms
+        h = n["mixer_in"].add_forward(resid32, delta)
+        y = self.mixer.forward(h, inputs, cache)
+        last = self.feed_forward is None
+        rounded = None
+        if not last and self._pair_fuses(n["mixer_out"], n["feed_forward_in"], resid32.shape[1]):
+            h = n["mixer_out"].normed_add_norm(resid32, y, n["feed_forward_in"])
+        else:
+            rounded = n["mixer_out"].normed_add(resid32, y, rounded=last and self.side is not None)
+            if not last:
+                h = n["feed_forward_in"].forward(resid32)
+        if not last:
+            y = self.feed_forward.forward(h, inputs)
+            rounded = n["feed_forward_out"].normed_add(resid32, y, rounded=self.side is not None)
+        if self.side is not None:
+            self.side.forward(resid32, rounded if rounded is not None else resid32, inputs)
+        return resid32, None

@@ -2,6 +2,9 @@
 one set of matrices; ``act`` is silu (SwiGLU) or the tanh form of gelu.  Reference: ``Qwen3MLP`` in
 ``acorninfer/models/qwen3.py:385-396``.
 gate and up are concatenated when bound: one matrix product gives ``[tokens, 2 I]``.
+
+Plain feed-forward (``dense``): ``down(act(up(x)))``, no gate, no bias; ``act`` one of ``ops.ACTIVATIONS``
+(the square of relu, the tanh form of gelu, silu, tanh).
 """
 
 from __future__ import annotations
@@ -78,3 +81,31 @@ class SwiGLU(FeedForward):
             h = ops.swiglu(gu, block=self.block, activation=self.activation)
         return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype, epilogue=epilogue,
                           residual32=residual32 if epilogue is None else None)
+
+
+@FEED_FORWARDS.register("dense")
+class DenseFeedForward(FeedForward):
+    graph_safe = True
+    adds_residual = True
+
+    def __init__(self, ctx: BuildContext, hidden_size: int, intermediate_size: int, activation: str = "relu_squared",
+                 names: dict | None = None):
+        """``names``: the up and down matrices' names relative to the part's prefix."""
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation must be one of {sorted(ops.ACTIVATIONS)}, got {activation!r}")
+        self.ctx, self.activation = ctx, activation
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.names = {"up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        return {self.names["up"]: TensorSpec((self.intermediate_size, self.hidden_size)),
+                self.names["down"]: TensorSpec((self.hidden_size, self.intermediate_size))}
+
+    def bind(self, tensors):
+        self.w_up = tensors[self.names["up"]].contiguous()
+        self.w_down = tensors[self.names["down"]].contiguous()
+
+    def forward(self, x, inputs, residual32=None):
+        h = ops.activation(ops.linear(x, self.w_up, out_dtype=self.ctx.dtype), self.activation)
+        return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype, residual32=residual32)

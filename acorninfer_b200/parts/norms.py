@@ -1,4 +1,5 @@
-"""RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` in float32, one rounding at the end; and LayerNorm with
+"""RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` in float32, one rounding at the end (``one_plus``: the stored
+weight is the distance of ``w`` from one); and LayerNorm with
 weight and bias: ``(x - mean) * rsqrt(var + eps) * w + b``, var the mean of the squared deviations.
 
 Reference: ``RMSNorm`` in ``acorninfer/models/qwen3.py:50-60`` (the weight multiplies in
@@ -19,21 +20,29 @@ from .base import NORMS, BuildContext, Norm, TensorSpec
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, ctx: BuildContext, width: int, eps: float, tensor: str = "weight"):
+    def __init__(self, ctx: BuildContext, width: int, eps: float, tensor: str = "weight", one_plus: bool = False):
         """``tensor``: the weight's name relative to the part's prefix ("" where the prefix is the
-        whole name)."""
+        whole name).  ``one_plus``: the tensor holds ``w - 1`` (values around zero); the norm multiplies by
+        ``1 + tensor``, the sum taken once, in float32, when the weight is bound."""
         self.ctx = ctx
         self.width = width
         self.eps = float(eps)
         self.tensor = tensor
+        self.one_plus = bool(one_plus)
         self.weight32: torch.Tensor | None = None
 
     def tensor_specs(self):
-        return {self.tensor: TensorSpec((self.width,), "norm")}
+        return {self.tensor: TensorSpec((self.width,), "norm_offset" if self.one_plus else "norm")}
 
     def bind(self, tensors):
         # Norm weights are held in float32 whatever they were stored as (widening is exact).
-        self.weight32 = tensors[self.tensor].to(torch.float32).contiguous()
+        w = tensors[self.tensor].to(torch.float32)
+        self.weight32 = (w + 1.0 if self.one_plus else w).contiguous()
+
+    def normed_add_norm(self, resid32, y, next_norm: "RMSNorm"):
+        """resid32 += norm(y) (in place), and ``next_norm`` of the new stream in the activation dtype: this
+        sublayer's output norm and the next sublayer's input norm in one kernel."""
+        return ops.rmsnorm_add_norm(resid32, y, self.weight32, self.eps, next_norm.weight32, next_norm.eps)
 
     def normed_add(self, resid32, y, rounded=True):
         """resid32 += norm(y) (in place): the norm of a sublayer's *output*, added to the stream.
