@@ -1356,7 +1356,8 @@ def token_shift(h: torch.Tensor, mu32: torch.Tensor, state: torch.Tensor, prev_o
     """``out[s, t] = h[t] + (prev[t] - h[t]) * mu32[s]`` for every blend s: ``prev`` is the row before ``t`` in its
     request, for a step's first token the float32 row kept in the request's state slot at ``prev_off`` (which
     ``conv_state_update`` with two taps keeps).  h [T, W]; mu32 [n, W]; returns [n, T, W] in h's dtype."""
-    _check(h, "h", None, 2)
+    if not h.is_cuda or h.dim() != 2:
+        raise KernelError("token_shift: h must be CUDA rows [T, W]")
     _check(mu32, "mu", torch.float32, 2)
     _check(state, "state", torch.float32, 2)
     T, W = h.shape
@@ -1376,7 +1377,8 @@ def wkv_prep(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
     gate ``silu(g)``.  r, k, v, g: [T, H dim] of the activation dtype with one row stride; z32 [T, H dim] float32."""
     T, C = r.shape
     for t, n in ((r, "r"), (k, "k"), (v, "v"), (g, "g")):
-        _check(t, n, r.dtype, 2)
+        if not t.is_cuda or t.dtype != r.dtype or t.dim() != 2:
+            raise KernelError(f"wkv_prep: {n} must be CUDA rows of one dtype")
         if t.shape != (T, C) or t.stride(0) != r.stride(0) or t.stride(1) != 1:
             raise KernelError("wkv_prep: r, k, v, g must have one shape and row stride")
     _check(z32, "z", torch.float32, 2)
@@ -1399,9 +1401,8 @@ def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
     """``act(x)`` elementwise over rows [T, n] (a row stride is allowed); float32 arithmetic, one rounding."""
     if kind not in ACTIVATIONS:
         raise KernelError(f"activation must be one of {sorted(ACTIVATIONS)}, got {kind!r}")
-    _check(x, "x", None, 2)
-    if x.stride(1) != 1:
-        raise KernelError("activation: rows must be contiguous")
+    if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("activation: x must be CUDA rows [T, n] with contiguous entries")
     out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     _ok(lib().acorn_activation(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], ACTIVATIONS[kind],
                                dtype_code(x.dtype), _stream()), "activation")

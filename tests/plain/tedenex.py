@@ -80,9 +80,11 @@ def attention(h, m, w, eps):
     positions: query i reads key j <= i of its own block only."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = conv_over_time(h @ w("q").T + w("q.b"), w("q.conv")).view(T, H, d)
-    k = conv_over_time(h @ w("k").T + w("k.b"), w("k.conv")).view(T, G, d)
-    v = conv_over_time(h @ w("v").T + w("v.b"), w("v.conv")).view(T, G, dv)
+    def project(name, heads, width):
+        u = h @ w(name).T + w(name + ".b")
+        return (conv_over_time(u, w(name + ".conv")) if m.get("conv") else u).view(T, heads, width)
+
+    q, k, v = project("q", H, d), project("k", G, d), project("v", G, dv)
     q = norm_plain(q, w("q.norm"), eps)
     k = norm_plain(k, w("k.norm"), eps)
     i = torch.arange(T)[:, None]
@@ -126,12 +128,14 @@ def wkv(h, m, w, eps):
 
 
 def latent_attention(h, m, w, eps):
-    """Attention whose queries, keys and values come through low-rank latents; a head's key is an up-projection
-    of the normed latent beside one rotated part that all heads share."""
+    """Attention whose keys and values (and, with ``q_rank``, queries) come through low-rank latents; a head's key
+    is an up-projection of the normed latent beside one rotated part that all heads share."""
     T = h.shape[0]
     H, d, r, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    cq = norm_plain(h @ w("dq").T, w("dq.norm"), eps)
-    q = (cq @ w("uq").T).view(T, H, d + r)
+    if m.get("q_rank") is not None:
+        q = (norm_plain(h @ w("dq").T, w("dq.norm"), eps) @ w("uq").T).view(T, H, d + r)
+    else:
+        q = (h @ w("q").T).view(T, H, d + r)
     qu, qr = q[..., :d], rotate_pairs(q[..., d:], m["rot"]["base"], m["rot"]["dims"])
     z = h @ w("dkv").T
     c = norm_plain(z[:, :rank], w("dkv.norm"), eps)
