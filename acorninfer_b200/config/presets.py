@@ -1,7 +1,7 @@
 """Sizes of published Qwen3 dense models as ``config.json`` dictionaries, for runs with random
 weights (benchmarks, the random-weights mode): no checkpoint is needed to measure at a model's
 layer sizes.  Only the keys the architecture reads are given.  For Kogonex, of which no model is
-published, two size sets with layers as wide as real models have them; the same for Vagulorn."""
+published, two size sets with layers as wide as real models have them; the same for Vagulorn and Tedenex."""
 
 from __future__ import annotations
 
@@ -80,6 +80,32 @@ def _vagulorn(width: int, vocab: int, heads: int, kv_heads: int, ff: int, span: 
 PRESETS.update({
     "vagulorn-w1024": _vagulorn(1024, 32768, heads=8, kv_heads=2, ff=3072, span=1024, ssm_heads=32, ssm_groups=4),
     "vagulorn-w2048": _vagulorn(2048, 65536, heads=16, kv_heads=4, ff=6144, span=1024, ssm_heads=64, ssm_groups=8),
+})
+
+
+def _tedenex(width: int, vocab: int, heads: int, kv_heads: int, ff: int, span: int, mix_heads: int, decay_rank: int,
+             lat_heads: int, rank: int, rot: int, q_rank: int, side: int, times: int = 2) -> dict:
+    """Layers in the pattern time mixing, convolved attention in blocks, latent attention, twice, the first three
+    run ``times`` times in a row; attention heads of 128, time-mixing heads of 64."""
+    mlp = {"kind": "dense", "ff": ff}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4, "mask": {"size": span}}
+    mix = {"heads": mix_heads, "dim": 64, "decay_rank": decay_rank}
+    lat = {"heads": lat_heads, "dim": 128, "rot_dim": rot, "vdim": 128, "kv_rank": rank, "q_rank": q_rank,
+           "scale": (128 + rot) ** -0.5, "rot": {"base": 1e6, "dims": rot}}
+    layers = []
+    for _ in range(2):
+        layers.append({"type": "wkv", "mixer": dict(mix), "mlp": mlp})
+        layers.append({"type": "attention", "mixer": dict(att), "mlp": mlp})
+        layers.append({"type": "latent_attention", "mixer": dict(lat), "mlp": mlp})
+    return {"architecture": "Tedenex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "token_side": {"dim": side},
+            "loop": {"start": 0, "stop": 3, "times": times}, "layers": layers}
+
+
+PRESETS.update({
+    "tedenex-w1024": _tedenex(1024, 32768, heads=8, kv_heads=2, ff=3072, span=1024, mix_heads=16, decay_rank=64, lat_heads=8,
+                              rank=192, rot=32, q_rank=384, side=128),
+    "tedenex-w2048": _tedenex(2048, 65536, heads=16, kv_heads=4, ff=6144, span=1024, mix_heads=32, decay_rank=64, lat_heads=16,
+                              rank=384, rot=64, q_rank=768, side=256),
 })
 
 

@@ -14,7 +14,7 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
                                       int table_stride, const int* token_row, const int* positions,
                                       const int* token_list, int n, int nq, int nkv, int d, int P, float scale,
                                       int window, int num_splits, float* part_o, float* part_lse,
-                                      int chunk, int keep, cudaStream_t stream);
+                                      int chunk, int keep, const float* slopes, cudaStream_t stream);
 
 // The scratch itself.  In host code this name is only a stand-in for the symbol, not a device
 // address: a kernel must be given what cudaGetSymbolAddress returns for it.
@@ -80,5 +80,5 @@ extern "C" int acorn_attention_decode_noalloc(const void* q, int64_t q_stride, v
     }
     return acorn_attention_decode(q, q_stride, out, k_pages, v_pages, block_table, page_base, table_stride, token_row,
                                   positions, token_list, n, nq, nkv, d, P, scale, window, num_splits, part_o, part_lse,
-                                  0, 0, stream);
+                                  0, 0, nullptr, stream);
 }
