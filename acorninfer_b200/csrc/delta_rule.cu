@@ -165,12 +165,25 @@ __device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
 // write, and sees the token itself through a bonus u per head and key channel: time mixing of the RWKV kind):
 //     o = S^T q + (sum_d q[d] u[d] k[d]) v,      S[d] = g[d] S[d] + k[d] v.
 // It is the same loop with gq = q, no sum against gk, beta = 1 and the bonus inside the k . q sum.
+//
+// In that form the state moves by S <- diag(g) S + k v^T, so a long row can be cut into segments that run side
+// by side (a recurrence is sequential over a row's tokens, and a prompt alone in its step would otherwise keep
+// a few dozen blocks busy): pass 1 runs every segment from a zero state to its end state E_j and multiplies up its
+// decays P_j; delta_fold walks the segments, S_j = diag(P_(j-1)) S_(j-1) + E_(j-1), leaving each segment's true
+// start state in the scratch and the row's end state in the request's slot; pass 2 runs every segment again from
+// its start state and writes the outputs.
+struct DeltaSegments {
+    int pass;                 // 0: rows in one piece; 1, 2: the passes above
+    int nseg, seg_len;        // segments a row, tokens a segment
+    float* seg_state;         // [rows * nseg, H, dim, vdim]
+    float* seg_decay;         // [rows * nseg, H, dim]
+};
 template <int DPT, int DELTA_SLICES, bool PRE>
 __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
     const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state, int64_t slot_stride,
     const int* __restrict__ row_start, const int* __restrict__ row_slot, float* __restrict__ out, int H, int KH, int dim,
-    int vdim, int stage, const float* __restrict__ bonus) {
+    int vdim, int stage, const float* __restrict__ bonus, DeltaSegments sg) {
     constexpr int DELTA_COLS = DELTA_THREADS / DELTA_SLICES;           // value channels a block
     extern __shared__ __align__(16) float sm[];
     constexpr int DIMP = DPT * DELTA_SLICES;                           // dim rounded up: entries beyond dim are zero
@@ -181,20 +194,27 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
     float* skq = sb + 2 * stage;                                       // [stage]
     pdl_wait();
     pdl_trigger();
-    const int r = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DELTA_COLS;
+    const int r = sg.pass ? blockIdx.x / sg.nseg : blockIdx.x, seg = sg.pass ? blockIdx.x % sg.nseg : 0;
+    const int h = blockIdx.y, c0 = blockIdx.z * DELTA_COLS;
     const int kh = h / (H / KH);
     const int slice = threadIdx.x & (DELTA_SLICES - 1), col = threadIdx.x / DELTA_SLICES;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int column = c0 + col;
     const bool live = column < vdim;
-    float* S_g = state + (int64_t)row_slot[r] * slot_stride + (int64_t)h * dim * vdim;
-    float S[DPT];
+    float* S_g = sg.pass ? sg.seg_state + (((int64_t)r * sg.nseg + seg) * H + h) * dim * vdim
+                         : state + (int64_t)row_slot[r] * slot_stride + (int64_t)h * dim * vdim;
+    float S[DPT], Pd[DPT];                                             // Pd: the segment's decays multiplied up (pass 1)
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = slice + DELTA_SLICES * i;
-        S[i] = (live && d < dim) ? S_g[(int64_t)d * vdim + column] : 0.f;
+        S[i] = (sg.pass != 1 && live && d < dim) ? S_g[(int64_t)d * vdim + column] : 0.f;
+        Pd[i] = 1.f;
     }
-    const int first = row_start[r], last = row_start[r + 1];
+    int first = row_start[r], last = row_start[r + 1];
+    if (sg.pass) {
+        first = min(last, first + seg * sg.seg_len);
+        last = min(last, first + sg.seg_len);
+    }
     const int stages = (last - first + stage - 1) / stage;
 
     auto fetch = [&](int s) {
@@ -267,26 +287,60 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
                 b += __shfl_xor_sync(0xffffffffu, b, o);
             }
             const float u = PRE ? v_s[tt * DELTA_COLS + col] : b_s[tt] * (v_s[tt * DELTA_COLS + col] - a);
-            if (slice == 0 && live) out[((int64_t)(t0 + tt) * H + h) * vdim + column] = fmaf(skq[tt], u, b);
+            if (slice == 0 && live && sg.pass != 1) out[((int64_t)(t0 + tt) * H + h) * vdim + column] = fmaf(skq[tt], u, b);
 #pragma unroll
             for (int i = 0; i < DPT; ++i) S[i] = fmaf(e[i].w, u, e[i].z * S[i]);
+            if (PRE && sg.pass == 1) {
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) Pd[i] *= e[i].z;
+            }
         }
         __syncthreads();                                               // pack and this stage's rows are free again
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
+    if (sg.pass == 2) return;                                          // the row's end state is delta_fold's
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = slice + DELTA_SLICES * i;
         if (live && d < dim) S_g[(int64_t)d * vdim + column] = S[i];
+        if (sg.pass == 1 && blockIdx.z == 0 && col == 0 && d < dim)
+            sg.seg_decay[(((int64_t)r * sg.nseg + seg) * H + h) * dim + d] = Pd[i];
+    }
+}
+
+// Per row, head and state entry: the segments' start states from their end states and decays (see above).
+__global__ void delta_fold_kernel(float* __restrict__ state, int64_t slot_stride, const int* __restrict__ row_slot,
+                                  float* __restrict__ seg_state, const float* __restrict__ seg_decay, int nseg, int H,
+                                  int dim, int vdim) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, h = blockIdx.y;
+    float* slot = state + (int64_t)row_slot[r] * slot_stride + (int64_t)h * dim * vdim;
+    for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < dim * vdim; e += gridDim.z * blockDim.x) {
+        const int d = e / vdim;
+        float cur = slot[e];
+        for (int j = 0; j < nseg; ++j) {
+            const int64_t at = ((int64_t)r * nseg + j) * H + h;
+            const float end = seg_state[at * dim * vdim + e];
+            seg_state[at * dim * vdim + e] = cur;
+            cur = fmaf(seg_decay[at * dim + d], cur, end);
+        }
+        slot[e] = cur;
     }
 }
 
 extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* vv, const float* beta, const float* g,
                                 float* state, int64_t slot_stride, const int* row_start, const int* row_slot, float* out,
-                                int rows, int H, int KH, int dim, int vdim, const float* bonus, cudaStream_t stream) {
+                                int rows, int H, int KH, int dim, int vdim, const float* bonus, int pass, int nseg,
+                                int seg_len, float* seg_state, float* seg_decay, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H > 65535 || vdim > 65535 || dim > 256 || H % KH) return ACORN_ERR_UNSUPPORTED;
     if (bonus == nullptr && beta == nullptr) return ACORN_ERR_UNSUPPORTED;
+    DeltaSegments sg = {pass, nseg, seg_len, seg_state, seg_decay};
+    if (pass != 0 && (bonus == nullptr || pass < 0 || pass > 2 || nseg < 1 || seg_len < 1 || seg_state == nullptr ||
+                      seg_decay == nullptr || (int64_t)rows * nseg > 0x7fffffff))
+        return ACORN_ERR_UNSUPPORTED;                   // segments fold only in the form that reads the state first
+    const int grid_rows = pass ? rows * nseg : rows;
     dim3 block(DELTA_THREADS);
     const int stage = dim <= 64 ? 32 : (dim <= 128 ? 16 : 8);
 #define DELTA_LAUNCH(N, SL)                                                                                                   \
@@ -297,7 +351,7 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
 #define DELTA_LAUNCH_AS(N, SL, PRE)                                                                                           \
     do {                                                                                                                      \
         const int cols = DELTA_THREADS / (SL);                                                                                \
-        dim3 grid(rows, H, (vdim + cols - 1) / cols);                                                                         \
+        dim3 grid(grid_rows, H, (vdim + cols - 1) / cols);                                                                    \
         const size_t smem = ((size_t)stage * (N) * (SL) * 4 + (size_t)2 * stage * 3 * dim + 2 * stage * cols + 3 * stage) *    \
                             sizeof(float);                                                                                    \
         static AcornPerDevice configured;                                                                                     \
@@ -308,7 +362,7 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
             configured.mark();                                                                                                \
         }                                                                                                                     \
         return acorn_launch(delta_rule_kernel<N, SL, PRE>, grid, block, smem, stream, qn, kn, vv, beta, g, state,             \
-                            slot_stride, row_start, row_slot, out, H, KH, dim, vdim, stage, bonus);                           \
+                            slot_stride, row_start, row_slot, out, H, KH, dim, vdim, stage, bonus, sg);                       \
     } while (0)
     // a thread holds few state entries (4; 8 for the widest heads): a warp is alone on its scheduler, so the
     // time of a token is the number of instructions a thread issues for it, and spreading a column over more
@@ -321,6 +375,16 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
     DELTA_LAUNCH(8, 32);
 #undef DELTA_LAUNCH
 #undef DELTA_LAUNCH_AS
+}
+
+extern "C" int acorn_delta_fold(float* state, int64_t slot_stride, const int* row_slot, float* seg_state,
+                                const float* seg_decay, int rows, int nseg, int H, int dim, int vdim, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H > 65535 || nseg < 1) return ACORN_ERR_UNSUPPORTED;
+    int bz = (dim * vdim + 255) / 256;
+    if (bz > 64) bz = 64;
+    return acorn_launch(delta_fold_kernel, dim3(rows, H, bz), dim3(256), 0, stream, state, slot_stride, row_slot, seg_state,
+                        seg_decay, nseg, H, dim, vdim);
 }
 
 // y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * gate   (w [vdim] shared by the heads: w_heads = 1; or one

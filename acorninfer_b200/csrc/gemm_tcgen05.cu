@@ -38,6 +38,8 @@ __device__ int g_gemm_tc_error = 0;
 #define TC_MODE_QKV_ROPE 3    // tiles are heads of 128: q/k RMSNorm + rotation; k and v to their cache pages
 #define TC_MODE_SWIGLU_PAIRS 4   // columns 2i and 2i + 1 are the gate and the up value of output i
 #define TC_MODE_GEGLU 5       // as TC_MODE_SWIGLU with the tanh form of gelu: out = gelu(gate) * up
+#define TC_MODE_RELU2 6       // out = max(product, 0)^2: the activation of a plain (ungated) feed-forward
+#define TC_MODE_TANH 7        // out = tanh(product)
 // reduction scratch of the epilogues (floats): four partial sums a row, or a head and its partial sums
 #define TC_RED_FLOATS(MB) (4 * (MB) > 256 ? 4 * (MB) : 256)
 
@@ -304,9 +306,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         for (int q = 1; q < 8; ++q) acc += v[q];
         return acc;
     };
-    if (p.mode == TC_MODE_PLAIN) {
+    if (p.mode == TC_MODE_PLAIN || p.mode == TC_MODE_RELU2 || p.mode == TC_MODE_TANH) {
         for (int i = 0, m = rank; m < m_valid; ++i, m += csize) {
-            const float val = tile_sum(i, col) * inv_s[m];
+            float val = tile_sum(i, col) * inv_s[m];
+            if (p.mode == TC_MODE_RELU2) { val = fmaxf(val, 0.f); val *= val; }
+            if (p.mode == TC_MODE_TANH) val = tanhf(val);
             if (n_ok) {
                 const int64_t o = (int64_t)(m0 + m) * p.ldo + n0 + col;
                 if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = val;
@@ -462,7 +466,8 @@ static int run_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, TcPara
     const int M = p.M, N = p.N, K = p.K;
     if (!acorn_gemm_tc_supported(M, N, K, ldx, ldw) || splits < 1 || splits > 8) return ACORN_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACORN_ERR_UNSUPPORTED;
-    if (p.mode != TC_MODE_PLAIN && (M > 64 || p.out_f32)) return ACORN_ERR_UNSUPPORTED;
+    if (p.mode != TC_MODE_PLAIN && p.mode != TC_MODE_RELU2 && p.mode != TC_MODE_TANH && (M > 64 || p.out_f32))
+        return ACORN_ERR_UNSUPPORTED;
     if (p.ss_in != nullptr && (M > 64 || p.ss_parts < 1 || p.norm_width < 1)) return ACORN_ERR_UNSUPPORTED;
     p.kblocks = (K + TC_BK - 1) / TC_BK;
     if (splits > p.kblocks) splits = p.kblocks;
@@ -489,7 +494,9 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
                                 int N, int K, int out_f32, int splits, int per_sm, int mode, const float* ss_in, int ss_parts,
                                 int norm_width, float eps, float* resid, int64_t ldr, const float* norm_w,
                                 float* ss_out, cudaStream_t stream) {
-    if (mode != TC_MODE_PLAIN && mode != TC_MODE_ADD_NORM && mode != TC_MODE_SWIGLU && mode != TC_MODE_GEGLU) return ACORN_ERR_UNSUPPORTED;
+    if (mode != TC_MODE_PLAIN && mode != TC_MODE_ADD_NORM && mode != TC_MODE_SWIGLU && mode != TC_MODE_GEGLU &&
+        mode != TC_MODE_RELU2 && mode != TC_MODE_TANH)
+        return ACORN_ERR_UNSUPPORTED;
     if ((mode == TC_MODE_SWIGLU || mode == TC_MODE_GEGLU) && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
     if (mode == TC_MODE_ADD_NORM && (resid == nullptr || norm_w == nullptr || ss_out == nullptr)) return ACORN_ERR_UNSUPPORTED;
     TcParams p = {};

@@ -29,12 +29,13 @@
 struct QkConv {
     const float* w;           // [channels, taps] or null: no convolution
     const float* bias;        // [channels] or null
-    const float* state;       // [slots, slot_stride] float32
+    float* state;             // [slots, slot_stride] float32
     int64_t slot_stride, conv_off;
     const int* row_start;
     const int* row_slot;
     int taps;                 // >= 1 when w is given
     int channels;             // nq d + nkv d + nkv dv
+    int update_single;        // a row of a single token shifts its own memory here (conv_state_update then skips such rows)
 };
 
 template <typename T>
@@ -75,11 +76,13 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
     }
     // element i of this head after bias and convolution (the plain element without them)
     int i0 = 0;
-    const float* cstate = nullptr;
+    float* cstate = nullptr;
+    bool shift = false;
     if (cv.w) {
         const int r = token_row[t];
         i0 = t - cv.row_start[r];                                         // the token's index within its row
         if (cv.taps > 1) cstate = cv.state + (int64_t)cv.row_slot[r] * cv.slot_stride + cv.conv_off;
+        shift = cv.update_single && cv.taps > 1 && cv.row_start[r + 1] - cv.row_start[r] == 1;
     }
     auto element = [&](int i) -> float {
         const float own = to_float(src[i]) + (cv.bias ? cv.bias[chan + i] : 0.f);
@@ -91,7 +94,10 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
             const float in = idx >= 0 ? to_float(src[(int64_t)(idx - i0) * ld + i]) + (cv.bias ? cv.bias[chan + i] : 0.f)
                                       : cstate[(int64_t)(cv.taps - 1 + idx) * cv.channels + chan + i];
             acc = fmaf(w[j], in, acc);
+            // the row's only token: a channel is read and written by this thread alone, oldest entry first
+            if (shift && j > 0) cstate[(int64_t)(j - 1) * cv.channels + chan + i] = in;
         }
+        if (shift) cstate[(int64_t)(cv.taps - 2) * cv.channels + chan + i] = own;
         return fmaf(w[cv.taps - 1], own, acc);
     };
     if (h >= nq + nkv) {   // value head: copy
@@ -242,14 +248,14 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
                                 const int* page_base, int table_stride, void* k_pages, void* v_pages,
                                 int tokens, int nq, int nkv, int d, int rot, int pairing, int P,
                                 float eps, int write_kv, int dtype, int64_t ld, int dv, int v_from_k,
-                                const float* conv_w, int taps, const float* bias, const float* state,
+                                const float* conv_w, int taps, const float* bias, float* state,
                                 int64_t slot_stride, int64_t conv_off, const int* row_start, const int* row_slot,
-                                void* q_out, int64_t ld_q, cudaStream_t stream) {
+                                void* q_out, int64_t ld_q, int update_single, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d > 1024 || rot > d || (rot & 1) || dv < 1 || dv > 1024 || (v_from_k && dv != d)) return ACORN_ERR_UNSUPPORTED;
     QkConv cv;
     cv.w = conv_w; cv.bias = bias; cv.state = state; cv.slot_stride = slot_stride; cv.conv_off = conv_off;
-    cv.row_start = row_start; cv.row_slot = row_slot; cv.taps = taps;
+    cv.row_start = row_start; cv.row_slot = row_slot; cv.taps = taps; cv.update_single = update_single;
     cv.channels = (nq + nkv) * d + (v_from_k ? 0 : nkv * dv);
     if (conv_w && (taps < 1 || taps > QK_MAX_TAPS || v_from_k || q_out == nullptr || row_start == nullptr ||
                    (taps > 1 && (state == nullptr || row_slot == nullptr))))

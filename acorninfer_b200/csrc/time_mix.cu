@@ -5,7 +5,9 @@
 //                     out[s][t] = h[t] + (prev[t] - h[t]) * mu[s],
 //                 prev of a step's first token from the request's state slot (float32 [W] at an offset:
 //                 the last row of the step before, zeros when the request starts; conv_state_update with
-//                 two taps keeps it).  One rounding to the activation type.
+//                 two taps keeps it; with update_single the kernel itself puts the row of a request that brings
+//                 a single token into its slot, and that kernel then skips such rows).  One rounding to the
+//                 activation type.
 //   wkv_prep      per token: float32 copies of r, k, v for the recurrence, the decay
 //                 exp(-exp(z + w0)) per head and key channel and the gate silu(g), all float32.
 #include "common.cuh"
@@ -14,35 +16,38 @@
 
 template <typename T>
 __global__ void token_shift_kernel(const T* __restrict__ h, int64_t ld, const float* __restrict__ mu,
-                                   const float* __restrict__ state, int64_t slot_stride, int64_t prev_off,
+                                   float* __restrict__ state, int64_t slot_stride, int64_t prev_off,
                                    const int* __restrict__ token_row, const int* __restrict__ row_start,
-                                   const int* __restrict__ row_slot, T* __restrict__ out, int64_t tokens, int W, int n) {
+                                   const int* __restrict__ row_slot, T* __restrict__ out, int64_t tokens, int W, int n,
+                                   int update_single) {
     pdl_wait();
     pdl_trigger();
     const int64_t t = blockIdx.x;
     const int r = token_row[t];
     const bool first = t == row_start[r];
-    const float* ps = state + (int64_t)row_slot[r] * slot_stride + prev_off;
+    const bool keep = update_single && first && row_start[r + 1] == t + 1;      // the row's only token: it is the next step's prev
+    float* ps = state + (int64_t)row_slot[r] * slot_stride + prev_off;
     const T* cur = h + t * ld;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         const float x = to_float(cur[i]);
         const float p = first ? ps[i] : to_float(cur[i - ld]);
         const float d = p - x;
+        if (keep) ps[i] = x;
 #pragma unroll
         for (int s = 0; s < SHIFT_MAX_BLENDS; ++s)
             if (s < n) out[((int64_t)s * tokens + t) * W + i] = from_float<T>(fmaf(d, mu[(int64_t)s * W + i], x));
     }
 }
 
-extern "C" int acorn_token_shift(const void* h, int64_t ld, const float* mu, const float* state, int64_t slot_stride,
+extern "C" int acorn_token_shift(const void* h, int64_t ld, const float* mu, float* state, int64_t slot_stride,
                                  int64_t prev_off, const int* token_row, const int* row_start, const int* row_slot,
-                                 void* out, int tokens, int W, int n, int dtype, cudaStream_t stream) {
+                                 void* out, int tokens, int W, int n, int dtype, int update_single, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (n < 1 || n > SHIFT_MAX_BLENDS) return ACORN_ERR_UNSUPPORTED;
     const int threads = W >= 1024 ? 256 : 128;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(token_shift_kernel<T>, dim3(tokens), dim3(threads), 0, stream,
                                                        (const T*)h, ld, mu, state, slot_stride, prev_off, token_row,
-                                                       row_start, row_slot, (T*)out, (int64_t)tokens, W, n));
+                                                       row_start, row_slot, (T*)out, (int64_t)tokens, W, n, update_single));
     return ACORN_ERR_UNSUPPORTED;
 }
 

@@ -109,7 +109,7 @@ class _Sigs:
     acorn_qk_rope_kv = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                         c_int, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
-                        c_void_p, c_void_p, c_int64, c_void_p]
+                        c_void_p, c_void_p, c_int64, c_int, c_void_p]
     acorn_attention_plain = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                              c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
@@ -121,7 +121,7 @@ class _Sigs:
     acorn_activation = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     acorn_side_gate = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_token_shift = [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
-                         c_int, c_int, c_int, c_int, c_void_p]
+                         c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_wkv_prep = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_latent_prep = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
@@ -138,7 +138,9 @@ class _Sigs:
     acorn_conv_state_update = [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int, c_int,
                                c_int, c_int, c_void_p, c_void_p]
     acorn_delta_rule = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
-                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                        c_void_p]
+    acorn_delta_fold = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_delta_out = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
     acorn_moe_route = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_moe_plan = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
@@ -483,19 +485,22 @@ def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: t
                                conv.state.stride(0) if conv is not None else 0, conv.offset if conv is not None else 0,
                                _ptr(conv.row_start) if conv is not None else None,
                                _ptr(conv.row_slot) if conv is not None else None,
-                               _ptr(q_out), q_out.stride(0) if q_out is not None else 0, _stream()),
+                               _ptr(q_out), q_out.stride(0) if q_out is not None else 0,
+                               1 if (conv is not None and conv.update_single) else 0, _stream()),
         "qk_rope_kv")
 
 
 class ShortConv:
     """What a short causal convolution over time needs of a step: the taps ``weight32`` [channels, taps]
     (float32, the last tap for the current token), the requests' state slots with the offset at which a
-    slot keeps the last ``taps - 1`` inputs ([taps - 1, channels] float32 in time order), and the step's rows."""
+    slot keeps the last ``taps - 1`` inputs ([taps - 1, channels] float32 in time order), and the step's rows.
+    ``update_single``: the kernel that convolves also shifts the memory of rows that bring a single token
+    (``conv_state_update(skip_single=True)`` then does the longer rows, and need not run when there are none)."""
 
     def __init__(self, weight32: torch.Tensor, state: torch.Tensor, offset: int, row_start: torch.Tensor,
-                 row_slot: torch.Tensor):
+                 row_slot: torch.Tensor, update_single: bool = False):
         self.weight32, self.state, self.offset = weight32, state, int(offset)
-        self.row_start, self.row_slot = row_start, row_slot
+        self.row_start, self.row_slot, self.update_single = row_start, row_slot, bool(update_single)
 
 
 def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -914,17 +919,22 @@ def rope_kv_fusable(num_rows: int, dtype: torch.dtype, head_dim: int, rotary_dim
     return dtype == torch.bfloat16 and num_rows > 0 and head_dim == 128 and rotary_dim == 128 and not interleaved
 
 
+TC_EPILOGUE_ACTS = {"relu_squared": 6, "tanh": 7}        # plain activations the one-CTA tcgen05 product applies itself (its mode)
+
+
 def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,
             out: torch.Tensor | None = None, epilogue: AddNormEpilogue | None = None, swiglu: bool = False,
             activation: str = "silu",
-            per_sm: int = 2):
+            per_sm: int = 2, act: str | None = None):
     """x [M, K] @ w [N, K]^T on tcgen05 tensor cores (bfloat16 in, float32 accumulate).
 
     ``x`` may be ``NormedRows`` (at most 64 rows): the rows' RMS factors are applied to the product.
     ``epilogue``: see ``AddNormEpilogue`` (returns ``NormedRows``).  ``swiglu``: ``w`` holds blocks
     of 64 gate rows and 64 up rows; returns ``act(gate) * up`` [M, N / 2], ``act`` by ``activation`` (silu or the
-    tanh form of gelu)."""
+    tanh form of gelu).  ``act`` (``"relu_squared"``, ``"tanh"``): a plain activation on the product, in its epilogue."""
     rows = x if isinstance(x, NormedRows) else None
+    if act is not None and (act not in TC_EPILOGUE_ACTS or epilogue is not None or swiglu):
+        raise KernelError(f"gemm_tc: activation {act!r} is not one of {sorted(TC_EPILOGUE_ACTS)}, or stands beside another epilogue")
     xt = rows.x if rows is not None else x
     if not gemm_tc_supported(xt, w):
         raise KernelError(f"gemm_tc does not take x {tuple(xt.shape)} {xt.dtype} stride {xt.stride()}, "
@@ -952,6 +962,8 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
         if N % 128 or out_dtype != torch.bfloat16:
             raise KernelError("gemm_tc: SwiGLU epilogue needs N a multiple of 128 and bfloat16 output")
         mode, out_cols = (2, 5)[GLU_ACTIVATIONS[activation]], N // 2
+    elif act is not None:
+        mode = TC_EPILOGUE_ACTS[act]
     if out is None:
         out = torch.empty((M, out_cols), dtype=out_dtype, device=xt.device)
     _check(out, "out", out_dtype, 2)
@@ -1038,7 +1050,8 @@ def fused_rows_ok(num_rows: int, dtype: torch.dtype, widths=None, num_sms: int =
 
 
 def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: AddNormEpilogue | None = None,
-           swiglu: bool = False, residual32: torch.Tensor | None = None, activation: str = "silu"):
+           swiglu: bool = False, residual32: torch.Tensor | None = None, activation: str = "silu",
+           act: str | None = None):
     """x [T, K] times w [N, K] transposed.
 
     float32 operands: the CUDA-core kernel (no reduced-precision matrix mode).
@@ -1053,7 +1066,16 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
     ``residual32`` ([T, N] float32) is an offer: where the product goes to the library it is
     added to ``residual32`` in place, in float32 (the library's C operand: the product is not
     rounded first), and None is returned; elsewhere the offer is ignored and the product returned.
+    ``act`` (a name of ``ACTIVATIONS``): a plain activation on the product: in the epilogue of the one-CTA
+    tcgen05 kernel where that runs and knows it, by the activation kernel after the product elsewhere.
     """
+    if act is not None:
+        if epilogue is not None or swiglu or residual32 is not None or isinstance(x, NormedRows):
+            raise KernelError("linear: a plain activation stands alone")
+        if (act in TC_EPILOGUE_ACTS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and x.shape[0] <= GEMM_TC_MAX_ROWS and gemm_tc_supported(x, w) and (out_dtype or x.dtype) == torch.bfloat16):
+            return gemm_tc(x, w, torch.bfloat16, act=act)
+        return activation_rows(linear(x, w, out_dtype), act)
     fused = isinstance(x, NormedRows) or epilogue is not None or swiglu
     xt = x.x if isinstance(x, NormedRows) else x
     out_dtype = out_dtype or xt.dtype
@@ -1152,6 +1174,18 @@ def rmsnorm_add_norm(resid32: torch.Tensor, y: torch.Tensor, weight32: torch.Ten
                                      out.data_ptr(), y.shape[0], H, float(eps), float(next_eps), dtype_code(y.dtype),
                                      _stream()), "rmsnorm_add_norm")
     return out
+
+
+class NormedPending:
+    """A sublayer's result whose RMS norm is still to be added to the stream: ``resid32 += rmsnorm(y) * weight32``.
+    A block hands it on so that the next block's first norm can be taken in the same kernel
+    (``rmsnorm_add_norm``); ``settle`` adds it where nobody takes it."""
+
+    def __init__(self, y: torch.Tensor, weight32: torch.Tensor, eps: float):
+        self.y, self.weight32, self.eps = y, weight32, float(eps)
+
+    def settle(self, resid32: torch.Tensor) -> None:
+        rmsnorm_add(resid32, self.y, self.weight32, self.eps, rounded=False)
 
 
 RMSNORM_ADD_NORM_MAX_WIDTH = 12288          # the updated row waits in shared memory (48 KB of float32)
@@ -1306,13 +1340,32 @@ def conv_state_update(main: torch.Tensor, state: torch.Tensor, conv_off: int, ro
         "conv_state_update")
 
 
+DELTA_MIN_SEGMENT = 64              # tokens: shorter segments are not worth a second pass
+DELTA_MAX_SEGMENTS = 16
+DELTA_ENOUGH_BLOCKS = 600           # blocks of 256 threads that keep the device busy
+
+
+def delta_segments(longest_row: int, num_rows: int, heads: int, dim: int, vdim: int) -> tuple[int, int]:
+    """(tokens a segment, segments a row) for the form of ``delta_rule`` that reads the state first; (0, 1): rows in
+    one piece.  Rows run side by side with heads and tiles of columns; where those are too few to fill the device
+    and a row is long, rows are cut into segments that run side by side, at the price of a second pass."""
+    cols = 256 // (4 if dim <= 16 else 8 if dim <= 32 else 16 if dim <= 128 else 32)
+    blocks = num_rows * heads * -(-vdim // cols)
+    nseg = min(DELTA_MAX_SEGMENTS, longest_row // DELTA_MIN_SEGMENT, -(-DELTA_ENOUGH_BLOCKS // blocks))
+    if nseg < 2:
+        return 0, 1
+    return -(-longest_row // nseg), nseg
+
+
 def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor | None, g: torch.Tensor,
                state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor, num_rows: int,
-               bonus32: torch.Tensor | None = None) -> torch.Tensor:
+               bonus32: torch.Tensor | None = None, longest_row: int | None = None) -> torch.Tensor:
     """The recurrence over every row's tokens from the state in its slot (updated in place): float32
     o [T, H, vdim].  With ``bonus32`` (float32 [H, dim]) and no ``beta`` the form without the delta correction
     whose output reads the state before the token's decay and write and sees the token itself through the
-    bonus: ``o = S^T q + (sum_d q_d bonus_d k_d) v;  S = diag(g) S + k v^T``."""
+    bonus: ``o = S^T q + (sum_d q_d bonus_d k_d) v;  S = diag(g) S + k v^T``.  In that form, with ``longest_row``
+    (the most tokens a row of the step brings, a host value), long rows of a step with few rows run in segments
+    side by side (``delta_segments``)."""
     T, H, vdim = v.shape
     KH, dim = q.shape[1], q.shape[2]
     if (beta is None) == (bonus32 is None):
@@ -1327,9 +1380,23 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
     if state.shape[1] < H * dim * vdim or g.shape != (T, H, dim) or dim > 256:
         raise KernelError(f"delta_rule: sizes do not fit (state {tuple(state.shape)}, H={H}, dim={dim}, vdim={vdim})")
     out = torch.empty((T, H, vdim), dtype=torch.float32, device=v.device)
-    _ok(lib().acorn_delta_rule(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(beta), g.data_ptr(), state.data_ptr(),
-                               state.stride(0), row_start.data_ptr(), row_slot.data_ptr(), out.data_ptr(), num_rows, H, KH,
-                               dim, vdim, _ptr(bonus32), _stream()), "delta_rule")
+    seg_len, nseg = delta_segments(longest_row, num_rows, H, dim, vdim) if (bonus32 is not None and longest_row) else (0, 1)
+
+    def run(pass_, seg_state=None, seg_decay=None):
+        _ok(lib().acorn_delta_rule(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(beta), g.data_ptr(), state.data_ptr(),
+                                   state.stride(0), row_start.data_ptr(), row_slot.data_ptr(), out.data_ptr(), num_rows, H,
+                                   KH, dim, vdim, _ptr(bonus32), pass_, nseg, max(seg_len, 1), _ptr(seg_state),
+                                   _ptr(seg_decay), _stream()), "delta_rule", f"pass {pass_}")
+
+    if nseg == 1:
+        run(0)
+        return out
+    seg_state = torch.empty((num_rows * nseg, H, dim, vdim), dtype=torch.float32, device=v.device)
+    seg_decay = torch.empty((num_rows * nseg, H, dim), dtype=torch.float32, device=v.device)
+    run(1, seg_state, seg_decay)
+    _ok(lib().acorn_delta_fold(state.data_ptr(), state.stride(0), row_slot.data_ptr(), seg_state.data_ptr(),
+                               seg_decay.data_ptr(), num_rows, nseg, H, dim, vdim, _stream()), "delta_fold")
+    run(2, seg_state, seg_decay)
     return out
 
 
@@ -1352,10 +1419,11 @@ def delta_out(o32: torch.Tensor, gate32: torch.Tensor, weight32: torch.Tensor, e
 
 
 def token_shift(h: torch.Tensor, mu32: torch.Tensor, state: torch.Tensor, prev_off: int, token_row: torch.Tensor,
-                row_start: torch.Tensor, row_slot: torch.Tensor) -> torch.Tensor:
+                row_start: torch.Tensor, row_slot: torch.Tensor, update_single: bool = False) -> torch.Tensor:
     """``out[s, t] = h[t] + (prev[t] - h[t]) * mu32[s]`` for every blend s: ``prev`` is the row before ``t`` in its
     request, for a step's first token the float32 row kept in the request's state slot at ``prev_off`` (which
-    ``conv_state_update`` with two taps keeps).  h [T, W]; mu32 [n, W]; returns [n, T, W] in h's dtype."""
+    ``conv_state_update`` with two taps keeps; with ``update_single`` this kernel keeps it for rows of a single
+    token, which that one then skips: ``skip_single``).  h [T, W]; mu32 [n, W]; returns [n, T, W] in h's dtype."""
     if not h.is_cuda or h.dim() != 2:
         raise KernelError("token_shift: h must be CUDA rows [T, W]")
     _check(mu32, "mu", torch.float32, 2)
@@ -1367,7 +1435,7 @@ def token_shift(h: torch.Tensor, mu32: torch.Tensor, state: torch.Tensor, prev_o
     out = torch.empty((n, T, W), dtype=h.dtype, device=h.device)
     _ok(lib().acorn_token_shift(h.data_ptr(), h.stride(0), mu32.data_ptr(), state.data_ptr(), state.stride(0), int(prev_off),
                                 token_row.data_ptr(), row_start.data_ptr(), row_slot.data_ptr(), out.data_ptr(), T, W, n,
-                                dtype_code(h.dtype), _stream()), "token_shift")
+                                dtype_code(h.dtype), 1 if update_single else 0, _stream()), "token_shift")
     return out
 
 
@@ -1395,6 +1463,10 @@ def wkv_prep(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
 # ------------------------------------------------------------------ plain activations, a token's side rows
 
 ACTIVATIONS = {"relu_squared": 0, "tanh": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def activation_rows(x: torch.Tensor, kind: str) -> torch.Tensor:
+    return activation(x, kind)
 
 
 def activation(x: torch.Tensor, kind: str) -> torch.Tensor:

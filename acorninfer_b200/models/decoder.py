@@ -177,6 +177,9 @@ class Decoder:
                                      "prepared this run's first norm")
                 if isinstance(delta, ops.DeltaPair):
                     delta = ops.fold_pair(resid32, delta)
+                if isinstance(delta, ops.NormedPending):
+                    delta.settle(resid32)
+                    delta = None
                 if delta is not None and not isinstance(delta, ops.RoundedRows):
                     ops.add_into(resid32, delta)
                 delta = None
@@ -191,6 +194,11 @@ class Decoder:
             taker = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else self.final_norm
             if isinstance(delta, ops.DeltaPair) and not getattr(taker, "accepts_pair", False):
                 delta = ops.fold_pair(resid32, delta)
+            # a normed sum left undone: the next block takes it into its first norm's kernel, or it is added here
+            if isinstance(delta, ops.NormedPending) and not (i + 1 < len(sched) and not sched[i + 1].add_embedding
+                                                             and getattr(taker, "accepts_normed_pending", False)):
+                delta.settle(resid32)
+                delta = None
         if inputs.num_logits == 0:
             return None
         if isinstance(delta, ops.RoundedRows):          # the last block already added its result

@@ -178,7 +178,7 @@ class Attention(Mixer):
             conv = None
             if self.taps:
                 conv = ops.ShortConv(self.conv32, cache.state if self.taps > 1 else proj.new_zeros((1, 0), dtype=torch.float32),
-                                     0, inputs.row_start, inputs.row_slot)
+                                     0, inputs.row_start, inputs.row_slot, update_single=True)
             ops.qk_rope_kv(proj, self.q_norm32, self.k_norm32,
                            pos.inv_freq if pos is not None else _no_freq(self.ctx.device),
                            inputs.positions, inputs.token_row, g.block_table, g.page_base,
@@ -186,9 +186,9 @@ class Attention(Mixer):
                            pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
                            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=True,
                            value_dim=self.dv, bias32=self.bias32, conv=conv, q_out=qkv)
-            if self.taps and self.taps > 1:
+            if self.taps and self.taps > 1 and inputs.plan.max_q_len > 1:     # rows of one token shifted their memory above
                 ops.conv_state_update(proj, cache.state, 0, inputs.row_start, inputs.row_slot, inputs.num_rows,
-                                      self.channels, self.taps, bias32=self.bias32)
+                                      self.channels, self.taps, bias32=self.bias32, skip_single=True)
         else:
             qkv = ops.linear(x, self.w_qkv, out_dtype=self.ctx.dtype)
             ops.qk_rope_kv(qkv, self.q_norm32, self.k_norm32,

@@ -271,7 +271,9 @@ class LayerExtra(Part):
     it.  ``forward(resid32, rows, inputs)`` adds its result to the float32 stream in place; ``rows`` is the
     stream as a sublayer reads it (rounded to the activation dtype; the stream itself under a float32 engine)."""
 
-    def forward(self, resid32: torch.Tensor, rows: torch.Tensor, inputs: "Any") -> None:
+    def forward(self, resid32: torch.Tensor, rows: torch.Tensor, inputs: "Any", defer: bool = False):
+        """``defer``: an extra whose last step is a normed sum into the stream may return it undone
+        (``ops.NormedPending``) instead, for the kernel of the norm that follows; otherwise None."""
         raise NotImplementedError
 
 

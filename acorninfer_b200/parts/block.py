@@ -157,13 +157,23 @@ class SandwichBlock(Block):
         return (hasattr(out_norm, "normed_add_norm") and hasattr(in_norm, "weight32")
                 and width <= ops.RMSNORM_ADD_NORM_MAX_WIDTH)
 
+    accepts_normed_pending = True       # takes an ``ops.NormedPending`` as what the block before still has to add
+
     def forward(self, resid32, delta, inputs, cache, next_norm=None):
         if isinstance(delta, ops.NormedRows):
             raise ValueError("a sandwich block cannot follow a block that fused the next norm into its last product")
         if isinstance(delta, ops.RoundedRows):          # the block before added its result itself
             delta = None
         n = self.norms
-        h = n["mixer_in"].add_forward(resid32, delta)
+        if isinstance(delta, ops.NormedPending):
+            # the normed sum the block before left undone, and this block's first norm, in one kernel
+            if hasattr(n["mixer_in"], "weight32") and resid32.shape[1] <= ops.RMSNORM_ADD_NORM_MAX_WIDTH:
+                h = ops.rmsnorm_add_norm(resid32, delta.y, delta.weight32, delta.eps, n["mixer_in"].weight32, n["mixer_in"].eps)
+            else:
+                delta.settle(resid32)
+                h = n["mixer_in"].forward(resid32)
+        else:
+            h = n["mixer_in"].add_forward(resid32, delta)
         y = self.mixer.forward(h, inputs, cache)
         last = self.feed_forward is None
         rounded = None
@@ -177,5 +187,5 @@ class SandwichBlock(Block):
             y = self.feed_forward.forward(h, inputs)
             rounded = n["feed_forward_out"].normed_add(resid32, y, rounded=self.side is not None)
         if self.side is not None:
-            self.side.forward(resid32, rounded if rounded is not None else resid32, inputs)
+            return resid32, self.side.forward(resid32, rounded if rounded is not None else resid32, inputs, defer=True)
         return resid32, None

@@ -107,5 +107,5 @@ class DenseFeedForward(FeedForward):
         self.w_down = tensors[self.names["down"]].contiguous()
 
     def forward(self, x, inputs, residual32=None):
-        h = ops.activation(ops.linear(x, self.w_up, out_dtype=self.ctx.dtype), self.activation)
+        h = ops.linear(x, self.w_up, out_dtype=self.ctx.dtype, act=self.activation)
         return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype, residual32=residual32)

@@ -43,9 +43,15 @@ class TokenSide(LayerExtra):
         self.w_proj = tensors[self.names["proj"]].contiguous()
         self.norm32 = tensors[self.names["norm"]].to(torch.float32).contiguous()
 
-    def forward(self, resid32, rows, inputs):
+    def forward(self, resid32, rows, inputs, defer: bool = False):
+        """``defer``: the normed sum is not taken here but handed back (``ops.NormedPending``) for the kernel of
+        the norm that follows."""
         dt = self.ctx.dtype
         z = ops.linear(rows, self.w_gate, out_dtype=dt)
         g = ops.side_gate(z, inputs.token_ids, self.table, self.index * self.dim)
         y = ops.linear(g, self.w_proj, out_dtype=dt)
-        ops.rmsnorm_add(resid32, y, self.norm32, self.eps, rounded=False)
+        pending = ops.NormedPending(y, self.norm32, self.eps)
+        if defer:
+            return pending
+        pending.settle(resid32)
+        return None

@@ -95,8 +95,11 @@ def test_presets_of_the_family_are_valid_configurations():
             assert cfg.head_dim == 128 and cfg.num_attention_heads % cfg.num_key_value_heads == 0
         elif name.startswith("kogonex"):
             assert len(cfg.layers) == 10 and cfg.layers[4].mixer.kv_from == 1
+        elif name.startswith("vagulorn"):
+            assert [l.type for l in cfg.layers[:4]] == ["mamba2", "attention", "parallel", "mamba2"]
         else:
-            assert name.startswith("vagulorn") and [l.type for l in cfg.layers[:4]] == ["mamba2", "attention", "parallel", "mamba2"]
+            assert name.startswith("tedenex") and [l.type for l in cfg.layers[:3]] == ["wkv", "attention", "latent_attention"]
+            assert len(spec_for(cfg).schedule) == 9          # the first three layers twice, then the other three
         spec_for(cfg)                                    # builds the model description
     assert preset("Qwen3-8B")["hidden_size"] == 4096
     import pytest

@@ -384,14 +384,19 @@ def test_attention_distance_penalty_in_blocks_of_positions(dtype, tol, kernel, d
     assert (got - want).abs().max() < tol
 
 
+@pytest.mark.parametrize("long", [False, True])
 @pytest.mark.parametrize("H,dim", [(3, 8), (1, 70), (2, 130), (4, 32), (2, 64)])
-def test_recurrence_that_reads_the_state_first_across_steps_and_slots(H, dim):
+def test_recurrence_that_reads_the_state_first_across_steps_and_slots(H, dim, long):
     """``o = S^T r + (r . u k) v;  S = diag(w) S + k v^T`` over rows of unequal length from states in scattered
     slots, in three steps (each continues the one before), against the loop; what lies behind S in a slot and
-    in other slots is left alone."""
+    in other slots is left alone.  ``long``: rows of hundreds of tokens, which run in segments side by side (rows
+    shorter than a segment, and of one token, beside them)."""
     o = ops()
     g = torch.Generator().manual_seed(dim)
     slots, cuts = [3, 0, 5], ([9, 1, 17], [1, 12, 2], [40, 1, 1])
+    if long:
+        cuts = ([700, 1, 130], [3, 400, 64], [1, 1, 300])
+        assert o.delta_segments(700, 3, H, dim, dim)[1] >= 3
     tail = 13
     state = torch.full((7, H * dim * dim + tail), 123.0, device=DEV)
     state[slots, :H * dim * dim] = 0
@@ -400,7 +405,8 @@ def test_recurrence_that_reads_the_state_first_across_steps_and_slots(H, dim):
     for r in range(3):
         T = sum(c[r] for c in cuts)
         seqs.append(dict(r=torch.randn(T, H, dim, generator=g).double(), k=torch.randn(T, H, dim, generator=g).double() * 0.5,
-                         v=torch.randn(T, H, dim, generator=g).double(), w=torch.rand(T, H, dim, generator=g).double() * 0.6 + 0.4))
+                         v=torch.randn(T, H, dim, generator=g).double(),
+                         w=torch.rand(T, H, dim, generator=g).double() * (0.1 if long else 0.6) + (0.9 if long else 0.4)))
     want = []
     for s in seqs:
         S = torch.zeros(H, dim, dim, dtype=torch.float64)
@@ -415,11 +421,11 @@ def test_recurrence_that_reads_the_state_first_across_steps_and_slots(H, dim):
     for lens in cuts:
         cat = lambda key: torch.cat([s[key][a:a + n] for s, a, n in zip(seqs, at, lens)]).float().contiguous().to(DEV)
         y = o.delta_rule(cat("r"), cat("k"), cat("v"), None, cat("w"), state, torch.tensor(np.cumsum([0] + lens), **i32),
-                         torch.tensor(slots, **i32), 3, bonus32=u.float().to(DEV)).cpu().double()
+                         torch.tensor(slots, **i32), 3, bonus32=u.float().to(DEV), longest_row=max(lens)).cpu().double()
         t0 = 0
         for r, n in enumerate(lens):
             ref = want[r][at[r]:at[r] + n]
-            assert (y[t0:t0 + n] - ref).abs().max() < 2e-4 * max(1.0, float(ref.abs().max())), (r, lens)
+            assert (y[t0:t0 + n] - ref).abs().max() < (1e-3 if long else 2e-4) * max(1.0, float(ref.abs().max())), (r, lens)
             t0 += n
             at[r] += n
     assert float(state[1].min()) == 123.0 and float(state[3, H * dim * dim:].min()) == 123.0
@@ -547,3 +553,19 @@ def test_activations_side_rows_norm_pairs_and_the_recurrence_inputs(dtype, tol):
     got = o.delta_out(o32.to(DEV), g32.to(DEV), wn.to(DEV), 1e-5, dtype).double().cpu()
     want = plain.rms(o32.double(), 1e-5).reshape(T, H * d) * wn.double() * g32.double().reshape(T, H * d)
     assert (got - want).abs().max() < tol * 4
+
+
+@pytest.mark.parametrize("M", [3, 32, 200])
+def test_plain_activations_on_a_product(M):
+    """The square of relu and tanh on a product: in the epilogue of the one-CTA tcgen05 kernel for few bfloat16 rows,
+    by the activation kernel after the product otherwise (more rows, float32)."""
+    o = ops()
+    g = torch.Generator().manual_seed(M)
+    K, N = 96, 136
+    x, w = torch.randn(M, K, generator=g) * 0.5, torch.randn(N, K, generator=g) * 0.2
+    for dtype, tol in ((torch.bfloat16, 3e-2), (torch.float32, 1e-5)):
+        xd, wd = x.to(dtype), w.to(dtype)
+        z = xd.double() @ wd.double().T
+        for act, f in (("relu_squared", plain.relu_squared), ("tanh", torch.tanh)):
+            got = o.linear(xd.to(DEV), wd.to(DEV), out_dtype=dtype, act=act).double().cpu()
+            assert got.shape == (M, N) and (got - f(z)).abs().max() < tol * max(1.0, float(f(z).abs().max())), (dtype, act)
