@@ -368,6 +368,15 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
     // time of a token is the number of instructions a thread issues for it, and spreading a column over more
     // lanes (up to a whole warp) shortens it although the reduction grows
     // (the tokens' staging is shared by a block's columns: 256 threads keep 8 to 64 columns together)
+    // rows in segments: the device is full of blocks, so what counts is the work all of them do for a token, and of
+    // that the reads of the packed entries from shared memory weigh most: a column over fewer lanes (more entries a
+    // thread, more columns a warp, which share the entries they read) halves them
+    if (pass != 0) {
+        if (dim <= 32) DELTA_LAUNCH_AS(8, 4, true);
+        if (dim <= 64) DELTA_LAUNCH_AS(8, 8, true);
+        if (dim <= 128) DELTA_LAUNCH_AS(16, 8, true);
+        DELTA_LAUNCH_AS(16, 16, true);
+    }
     if (dim <= 16) DELTA_LAUNCH(4, 4);
     if (dim <= 32) DELTA_LAUNCH(4, 8);
     if (dim <= 64) DELTA_LAUNCH(4, 16);

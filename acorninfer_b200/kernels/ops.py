@@ -1349,7 +1349,7 @@ def delta_segments(longest_row: int, num_rows: int, heads: int, dim: int, vdim: 
     """(tokens a segment, segments a row) for the form of ``delta_rule`` that reads the state first; (0, 1): rows in
     one piece.  Rows run side by side with heads and tiles of columns; where those are too few to fill the device
     and a row is long, rows are cut into segments that run side by side, at the price of a second pass."""
-    cols = 256 // (4 if dim <= 16 else 8 if dim <= 32 else 16 if dim <= 128 else 32)
+    cols = 256 // (4 if dim <= 32 else 8 if dim <= 128 else 16)         # columns a block of the segmented passes takes
     blocks = num_rows * heads * -(-vdim // cols)
     nseg = min(DELTA_MAX_SEGMENTS, longest_row // DELTA_MIN_SEGMENT, -(-DELTA_ENOUGH_BLOCKS // blocks))
     if nseg < 2:
