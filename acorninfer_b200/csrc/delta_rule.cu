@@ -178,13 +178,14 @@ struct DeltaSegments {
     float* seg_state;         // [rows * nseg, H, dim, vdim]
     float* seg_decay;         // [rows * nseg, H, dim]
 };
-template <int DPT, int DELTA_SLICES, bool PRE>
-__global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
+// CPT: columns a thread holds (an entry read from shared memory then serves them all); NT: threads a block.
+template <int DPT, int DELTA_SLICES, bool PRE, int CPT, int NT>
+__global__ void __launch_bounds__(NT) delta_rule_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
     const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ state, int64_t slot_stride,
     const int* __restrict__ row_start, const int* __restrict__ row_slot, float* __restrict__ out, int H, int KH, int dim,
     int vdim, int stage, const float* __restrict__ bonus, DeltaSegments sg) {
-    constexpr int DELTA_COLS = DELTA_THREADS / DELTA_SLICES;           // value channels a block
+    constexpr int DELTA_COLS = NT / DELTA_SLICES * CPT;                // value channels a block
     extern __shared__ __align__(16) float sm[];
     constexpr int DIMP = DPT * DELTA_SLICES;                           // dim rounded up: entries beyond dim are zero
     float4* pack = reinterpret_cast<float4*>(sm);                      // [stage][DIMP]: gk, gq, g, k
@@ -199,15 +200,18 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
     const int kh = h / (H / KH);
     const int slice = threadIdx.x & (DELTA_SLICES - 1), col = threadIdx.x / DELTA_SLICES;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int column = c0 + col;
-    const bool live = column < vdim;
+    const int column = c0 + col * CPT;                                 // the first of this thread's columns
+    bool live[CPT];
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) live[j] = column + j < vdim;
     float* S_g = sg.pass ? sg.seg_state + (((int64_t)r * sg.nseg + seg) * H + h) * dim * vdim
                          : state + (int64_t)row_slot[r] * slot_stride + (int64_t)h * dim * vdim;
-    float S[DPT], Pd[DPT];                                             // Pd: the segment's decays multiplied up (pass 1)
+    float S[CPT][DPT], Pd[DPT];                                        // Pd: the segment's decays multiplied up (pass 1)
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = slice + DELTA_SLICES * i;
-        S[i] = (sg.pass != 1 && live && d < dim) ? S_g[(int64_t)d * vdim + column] : 0.f;
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) S[j][i] = (sg.pass != 1 && live[j] && d < dim) ? S_g[(int64_t)d * vdim + column + j] : 0.f;
         Pd[i] = 1.f;
     }
     int first = row_start[r], last = row_start[r + 1];
@@ -254,7 +258,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
             }
             pack[e] = v;
         }
-        for (int tt = warp; tt < n; tt += DELTA_THREADS / 32) {
+        for (int tt = warp; tt < n; tt += NT / 32) {
             float kq = 0.f;
             for (int d = lane; d < dim; d += 32) {
                 const float qd = PRE ? rw[(tt * 3 + 0) * dim + d] * bonus[(int64_t)h * dim + d] : rw[(tt * 3 + 0) * dim + d];
@@ -272,24 +276,29 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
             float4 e[DPT];
 #pragma unroll
             for (int i = 0; i < DPT; ++i) e[i] = p[DELTA_SLICES * i];
-            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < DPT; i += 2) {
-                if (!PRE) a0 = fmaf(S[i], e[i].x, a0);
-                b0 = fmaf(S[i], e[i].y, b0);
-                if (!PRE) a1 = fmaf(S[i + 1], e[i + 1].x, a1);
-                b1 = fmaf(S[i + 1], e[i + 1].y, b1);
+            for (int j = 0; j < CPT; ++j) {
+                float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT; i += 2) {
+                    if (!PRE) a0 = fmaf(S[j][i], e[i].x, a0);
+                    b0 = fmaf(S[j][i], e[i].y, b0);
+                    if (!PRE) a1 = fmaf(S[j][i + 1], e[i + 1].x, a1);
+                    b1 = fmaf(S[j][i + 1], e[i + 1].y, b1);
+                }
+                float a = a0 + a1, b = b0 + b1;
+#pragma unroll
+                for (int o = 1; o < DELTA_SLICES; o <<= 1) {
+                    if (!PRE) a += __shfl_xor_sync(0xffffffffu, a, o);
+                    b += __shfl_xor_sync(0xffffffffu, b, o);
+                }
+                const float vj = v_s[tt * DELTA_COLS + col * CPT + j];
+                const float u = PRE ? vj : b_s[tt] * (vj - a);
+                if (slice == 0 && live[j] && sg.pass != 1)
+                    out[((int64_t)(t0 + tt) * H + h) * vdim + column + j] = fmaf(skq[tt], u, b);
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) S[j][i] = fmaf(e[i].w, u, e[i].z * S[j][i]);
             }
-            float a = a0 + a1, b = b0 + b1;
-#pragma unroll
-            for (int o = 1; o < DELTA_SLICES; o <<= 1) {
-                if (!PRE) a += __shfl_xor_sync(0xffffffffu, a, o);
-                b += __shfl_xor_sync(0xffffffffu, b, o);
-            }
-            const float u = PRE ? v_s[tt * DELTA_COLS + col] : b_s[tt] * (v_s[tt * DELTA_COLS + col] - a);
-            if (slice == 0 && live && sg.pass != 1) out[((int64_t)(t0 + tt) * H + h) * vdim + column] = fmaf(skq[tt], u, b);
-#pragma unroll
-            for (int i = 0; i < DPT; ++i) S[i] = fmaf(e[i].w, u, e[i].z * S[i]);
             if (PRE && sg.pass == 1) {
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) Pd[i] *= e[i].z;
@@ -302,7 +311,9 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = slice + DELTA_SLICES * i;
-        if (live && d < dim) S_g[(int64_t)d * vdim + column] = S[i];
+#pragma unroll
+        for (int j = 0; j < CPT; ++j)
+            if (live[j] && d < dim) S_g[(int64_t)d * vdim + column + j] = S[j][i];
         if (sg.pass == 1 && blockIdx.z == 0 && col == 0 && d < dim)
             sg.seg_decay[(((int64_t)r * sg.nseg + seg) * H + h) * dim + d] = Pd[i];
     }
@@ -341,27 +352,28 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
                       seg_decay == nullptr || (int64_t)rows * nseg > 0x7fffffff))
         return ACORN_ERR_UNSUPPORTED;                   // segments fold only in the form that reads the state first
     const int grid_rows = pass ? rows * nseg : rows;
-    dim3 block(DELTA_THREADS);
     const int stage = dim <= 64 ? 32 : (dim <= 128 ? 16 : 8);
 #define DELTA_LAUNCH(N, SL)                                                                                                   \
     do {                                                                                                                      \
-        if (bonus) DELTA_LAUNCH_AS(N, SL, true);                                                                              \
-        DELTA_LAUNCH_AS(N, SL, false);                                                                                        \
+        if (bonus) DELTA_LAUNCH_AS(N, SL, true, 1, DELTA_THREADS);                                                            \
+        DELTA_LAUNCH_AS(N, SL, false, 1, DELTA_THREADS);                                                                      \
     } while (0)
-#define DELTA_LAUNCH_AS(N, SL, PRE)                                                                                           \
+#define DELTA_LAUNCH_AS(N, SL, PRE, CPT, NT)                                                                                  \
     do {                                                                                                                      \
-        const int cols = DELTA_THREADS / (SL);                                                                                \
+        const int cols = (NT) / (SL) * (CPT);                                                                                 \
+        dim3 block(NT);                                                                                                       \
         dim3 grid(grid_rows, H, (vdim + cols - 1) / cols);                                                                    \
         const size_t smem = ((size_t)stage * (N) * (SL) * 4 + (size_t)2 * stage * 3 * dim + 2 * stage * cols + 3 * stage) *    \
                             sizeof(float);                                                                                    \
         static AcornPerDevice configured;                                                                                     \
         if (!configured.seen()) {                                                                                             \
-            cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<N, SL, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+            cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<N, SL, PRE, CPT, NT>,                                      \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,                                 \
                                                  100 * 1024);                                                                 \
             if (e != cudaSuccess) return (int)e;                                                                              \
             configured.mark();                                                                                                \
         }                                                                                                                     \
-        return acorn_launch(delta_rule_kernel<N, SL, PRE>, grid, block, smem, stream, qn, kn, vv, beta, g, state,             \
+        return acorn_launch(delta_rule_kernel<N, SL, PRE, CPT, NT>, grid, block, smem, stream, qn, kn, vv, beta, g, state,    \
                             slot_stride, row_start, row_slot, out, H, KH, dim, vdim, stage, bonus, sg);                       \
     } while (0)
     // a thread holds few state entries (4; 8 for the widest heads): a warp is alone on its scheduler, so the
@@ -370,12 +382,12 @@ extern "C" int acorn_delta_rule(const float* qn, const float* kn, const float* v
     // (the tokens' staging is shared by a block's columns: 256 threads keep 8 to 64 columns together)
     // rows in segments: the device is full of blocks, so what counts is the work all of them do for a token, and of
     // that the reads of the packed entries from shared memory weigh most: a column over fewer lanes (more entries a
-    // thread, more columns a warp, which share the entries they read) halves them
+    // thread, more columns a warp, which share the entries they read) and several columns a thread cut them down
     if (pass != 0) {
-        if (dim <= 32) DELTA_LAUNCH_AS(8, 4, true);
-        if (dim <= 64) DELTA_LAUNCH_AS(8, 8, true);
-        if (dim <= 128) DELTA_LAUNCH_AS(16, 8, true);
-        DELTA_LAUNCH_AS(16, 16, true);
+        if (dim <= 32) DELTA_LAUNCH_AS(8, 4, true, 1, 256);
+        if (dim <= 64) DELTA_LAUNCH_AS(8, 8, true, 4, 128);
+        if (dim <= 128) DELTA_LAUNCH_AS(16, 8, true, 2, 256);
+        DELTA_LAUNCH_AS(16, 16, true, 1, 256);
     }
     if (dim <= 16) DELTA_LAUNCH(4, 4);
     if (dim <= 32) DELTA_LAUNCH(4, 8);
