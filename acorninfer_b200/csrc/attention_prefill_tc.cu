@@ -63,12 +63,13 @@ struct AttnTcParams {
 #define ATC_NUM_BARS (1 + 2 * ATC_SLOTS + 2 + 2 + 2)
 #define ATC_TMEM_COLS 512
 
-// s[c] -= step * (qpos - (key0 + c)): a penalty on the distance to the key, in units of the raw score
-// (the slope divided by the softmax scale), so that the scaled exponent below holds it
-__device__ __forceinline__ void atc_distance(float (&s)[64], int key0, int qpos, float step) {
-    const float base = (float)(qpos - key0);
+// s[c] += step * (c0 + c): the part of the penalty on the distance to the key that differs between a row's
+// columns, in units of the raw score (the slope divided by the softmax scale); the row's own part,
+// -step * (qpos - key0), rides in the exponent's offset and is added to the block's maximum
+template <int C0>
+__device__ __forceinline__ void atc_distance(float (&s)[64], float step) {
 #pragma unroll
-    for (int c = 0; c < 64; ++c) s[c] = fmaf(-step, base - (float)c, s[c]);
+    for (int c = 0; c < 64; ++c) s[c] = fmaf(step, (float)(C0 + c), s[c]);
 }
 
 // -inf where the query at qpos may not see the key (causal, the first key its window or its block of positions
@@ -168,7 +169,10 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
     // block j holds keys from j * 128 (j < nkb) or from lo + (j - nkb) * 128
     const int nkb = (p.keep > 0 && lo > 0) ? min((p.keep + ATC_BN - 1) / ATC_BN, lo / ATC_BN) : 0;
     const int nb = nkb + (hi - lo + ATC_BN - 1) / ATC_BN;
-#define ATC_KEY0(j) ((j) < nkb ? (j) * ATC_BN : lo + ((j) - nkb) * ATC_BN)
+    // With a distance penalty the nearest keys weigh most: the rule's blocks are then walked from the last to the
+    // first, so that a row's reference maximum is set by its first block and the later ones need no second pass.
+    const bool rev = p.slopes != nullptr;
+#define ATC_KEY0(j) ((j) < nkb ? (j) * ATC_BN : lo + (rev ? nb - 1 - (j) : (j) - nkb) * ATC_BN)
 
     if (warp == 8) {
         // ---------------------------------------------------------------- producer
@@ -311,16 +315,18 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             // reference, and then the warp reads the block again.
             float s[64];
             uint32_t w_lo[32], w_hi[32];
-            float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
+            // the row's part of the distance penalty, in raw score units and in the exponent's
+            const float off = sloped ? -dist_step * (float)(qpos - key0) : 0.f, off2 = off * p.scale_log2;
+            float neg_ref = (m_ref == -INFINITY ? 0.f : -m_ref) + off2;
             tmem_ld64(my_s, s);
-            if (sloped) atc_distance(s, key0, qpos, dist_step);
+            if (sloped) atc_distance<0>(s, dist_step);
             if (masked) atc_mask(s, key0, qpos, row_ok, first_seen, p.keep);
             float mx = atc_max(s);
             float psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             tmem_ld64(my_s + 64, s);
-            if (sloped) atc_distance(s, key0 + 64, qpos, dist_step);
+            if (sloped) atc_distance<64>(s, dist_step);
             if (masked) atc_mask(s, key0 + 64, qpos, row_ok, first_seen, p.keep);
-            mx = fmaxf(mx, atc_max(s)) * p.scale_log2;                   // the scale is positive
+            mx = (fmaxf(mx, atc_max(s)) + off) * p.scale_log2;           // the scale is positive
             float corr = 1.f;
             const bool grew = mx > m_ref + ATC_RESCALE_LOG2;
             if (__any_sync(0xffffffffu, grew)) {
@@ -328,11 +334,11 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
                     corr = fast_exp2(m_ref - mx);                        // m_ref = -inf: 0
                     l_run *= corr;
                     m_ref = mx;
-                    neg_ref = -m_ref;
+                    neg_ref = off2 - m_ref;
                 }
                 psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
                 tmem_ld64(my_s, s);
-                if (sloped) atc_distance(s, key0, qpos, dist_step);
+                if (sloped) atc_distance<0>(s, dist_step);
                 if (masked) atc_mask(s, key0, qpos, row_ok, first_seen, p.keep);
                 psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             } else {
