@@ -144,9 +144,61 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T* __restrict__ 
     }
 }
 
+// The same for few tokens (a decode step): a block takes a head, up to HLR_TM tokens (their x rows wait in shared
+// memory as float32) and a run of outputs; a warp takes an output at a time, its lanes four weights each per 128
+// inputs (8- or 16-byte reads), and reduces the tokens' partial sums by shuffles.  A token's chain of sums is fixed
+// by the lane partition, so its result does not depend on the other tokens here either.
+#define HLR_TM 8
+template <typename T>
+__global__ void __launch_bounds__(256) head_linear_rows_kernel(const T* __restrict__ x, int64_t xs_t, int64_t xs_h,
+                                                               const T* __restrict__ w, T* __restrict__ y, int64_t ys_t,
+                                                               int64_t ys_h, int tokens, int O, int I, int rows_per_block) {
+    extern __shared__ __align__(16) float hlr_x[];                 // [HLR_TM][I]
+    pdl_wait();
+    pdl_trigger();
+    const int h = blockIdx.y, t0 = blockIdx.z * HLR_TM;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e = threadIdx.x; e < HLR_TM * I; e += 256) {
+        const int tt = e / I, i = e - tt * I;
+        hlr_x[e] = (t0 + tt < tokens) ? to_float(x[(int64_t)(t0 + tt) * xs_t + (int64_t)h * xs_h + i]) : 0.f;
+    }
+    __syncthreads();
+    const T* wh = w + (int64_t)h * O * I;
+    const int o_end = min(O, (int)(blockIdx.x + 1) * rows_per_block);
+    for (int o = blockIdx.x * rows_per_block + warp; o < o_end; o += 8) {
+        const T* wr = wh + (int64_t)o * I;
+        float acc[HLR_TM];
+#pragma unroll
+        for (int t = 0; t < HLR_TM; ++t) acc[t] = 0.f;
+        for (int i0 = lane * 4; i0 < I; i0 += 128) {
+            const float4 wv = Vec4<T>::load(wr + i0);
+#pragma unroll
+            for (int t = 0; t < HLR_TM; ++t) {
+                const float4 a = *reinterpret_cast<const float4*>(hlr_x + t * I + i0);
+                acc[t] = fmaf(wv.x, a.x, fmaf(wv.y, a.y, fmaf(wv.z, a.z, fmaf(wv.w, a.w, acc[t]))));
+            }
+        }
+        float mine = 0.f;
+#pragma unroll
+        for (int t = 0; t < HLR_TM; ++t) {
+            const float v = warp_sum(acc[t]);
+            if (lane == t) mine = v;
+        }
+        if (lane < HLR_TM && t0 + lane < tokens) y[(int64_t)(t0 + lane) * ys_t + (int64_t)h * ys_h + o] = from_float<T>(mine);
+    }
+}
+#define HLR_MAX_TOKENS 32
+
 extern "C" int acorn_head_linear(const void* x, int64_t xs_t, int64_t xs_h, const void* w, void* y, int64_t ys_t,
                                  int64_t ys_h, int tokens, int H, int O, int I, int dtype, cudaStream_t stream) {
     if (tokens <= 0 || H <= 0 || O <= 0) return 0;
+    if (tokens <= HLR_MAX_TOKENS && I % 4 == 0 && (size_t)HLR_TM * I * sizeof(float) <= 48 * 1024 && H <= 65535) {
+        const int rpb = (int64_t)H * ((O + 7) / 8) >= 592 ? 16 : 8;
+        dim3 grid((O + rpb - 1) / rpb, H, (tokens + HLR_TM - 1) / HLR_TM);
+        const size_t smem = (size_t)HLR_TM * I * sizeof(float);
+        ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(head_linear_rows_kernel<T>, grid, dim3(256), smem, stream, (const T*)x,
+                                                           xs_t, xs_h, (const T*)w, (T*)y, ys_t, ys_h, tokens, O, I, rpb));
+    }
     if (H > 65535 || (O + HL_TN - 1) / HL_TN > 65535) return ACORN_ERR_UNSUPPORTED;
     dim3 grid((tokens + HL_TM - 1) / HL_TM, (O + HL_TN - 1) / HL_TN, H);
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(head_linear_kernel<T>, grid, dim3(256), 0, stream, (const T*)x, xs_t,

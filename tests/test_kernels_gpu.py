@@ -134,3 +134,26 @@ def test_gemm_f32_shows_what_a_reduced_precision_mode_would_hide():
     a = torch.full((4, 8), 1 + 2 ** -12, device=DEV)
     w = torch.eye(8, device=DEV)
     assert torch.equal(ops().gemm_f32(a, w), a)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,O,I", [(1, 3, 40, 24), (8, 16, 384, 128), (9, 2, 128, 384), (5, 4, 7, 20), (32, 2, 50, 132),
+                                     (33, 2, 50, 132), (6, 3, 10, 18), (200, 2, 96, 48)])
+def test_per_head_products_of_few_and_many_tokens(dtype, T, H, O, I):
+    """y[t, h] = w[h] x[t, h] through views with token and head strides; few tokens (the kernel of decode steps),
+    inputs that are no multiple of four (the tiled kernel), many tokens; a token's result does not depend on the
+    others of its step."""
+    g = torch.Generator(device=DEV).manual_seed(T * 1000 + O)
+    xbuf = torch.randn(T, H, I + 6, device=DEV, generator=g).to(dtype)
+    ybuf = torch.zeros(T, H, O + 3, device=DEV, dtype=dtype)
+    w = (torch.randn(H, O, I, device=DEV, generator=g) / math.sqrt(I)).to(dtype)
+    x, y = xbuf[:, :, :I], ybuf[:, :, 2:2 + O]
+    ops().head_linear(x, w, y)
+    ref = torch.einsum("hoi,thi->tho", w.double(), x.double())
+    t = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(y.double(), ref, **t)
+    assert float(ybuf[:, :, :2].abs().max()) == 0 and float(ybuf[:, :, 2 + O:].abs().max()) == 0
+    if T <= 32:
+        y1 = torch.zeros(1, H, O, device=DEV, dtype=dtype)
+        ops().head_linear(x[T - 1:], w, y1)
+        assert torch.equal(y1[0], y[T - 1])
