@@ -278,19 +278,23 @@ __global__ void __launch_bounds__(NT) delta_rule_kernel(
             for (int i = 0; i < DPT; ++i) e[i] = p[DELTA_SLICES * i];
 #pragma unroll
             for (int j = 0; j < CPT; ++j) {
-                float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+                float a = 0.f, b = 0.f;
+                if (!PRE || sg.pass != 1) {                            // a segment's first pass writes no output
+                    float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-                for (int i = 0; i < DPT; i += 2) {
-                    if (!PRE) a0 = fmaf(S[j][i], e[i].x, a0);
-                    b0 = fmaf(S[j][i], e[i].y, b0);
-                    if (!PRE) a1 = fmaf(S[j][i + 1], e[i + 1].x, a1);
-                    b1 = fmaf(S[j][i + 1], e[i + 1].y, b1);
-                }
-                float a = a0 + a1, b = b0 + b1;
+                    for (int i = 0; i < DPT; i += 2) {
+                        if (!PRE) a0 = fmaf(S[j][i], e[i].x, a0);
+                        b0 = fmaf(S[j][i], e[i].y, b0);
+                        if (!PRE) a1 = fmaf(S[j][i + 1], e[i + 1].x, a1);
+                        b1 = fmaf(S[j][i + 1], e[i + 1].y, b1);
+                    }
+                    a = a0 + a1;
+                    b = b0 + b1;
 #pragma unroll
-                for (int o = 1; o < DELTA_SLICES; o <<= 1) {
-                    if (!PRE) a += __shfl_xor_sync(0xffffffffu, a, o);
-                    b += __shfl_xor_sync(0xffffffffu, b, o);
+                    for (int o = 1; o < DELTA_SLICES; o <<= 1) {
+                        if (!PRE) a += __shfl_xor_sync(0xffffffffu, a, o);
+                        b += __shfl_xor_sync(0xffffffffu, b, o);
+                    }
                 }
                 const float vj = v_s[tt * DELTA_COLS + col * CPT + j];
                 const float u = PRE ? vj : b_s[tt] * (vj - a);

@@ -40,6 +40,7 @@ __device__ int g_gemm_tc_error = 0;
 #define TC_MODE_GEGLU 5       // as TC_MODE_SWIGLU with the tanh form of gelu: out = gelu(gate) * up
 #define TC_MODE_RELU2 6       // out = max(product, 0)^2: the activation of a plain (ungated) feed-forward
 #define TC_MODE_TANH 7        // out = tanh(product)
+#define TC_MODE_GELU_ROWS 8   // out = gelu_tanh(product) * rows[ids[m], col0 + n]: a gate on columns of a row chosen per token
 // reduction scratch of the epilogues (floats): four partial sums a row, or a head and its partial sums
 #define TC_RED_FLOATS(MB) (4 * (MB) > 256 ? 4 * (MB) : 256)
 
@@ -77,6 +78,11 @@ struct TcParams {
     // turn (at most g_tiles; a CTA beyond the last one leaves at once).  K is not split.
     const int* g_offsets;
     int g_experts, g_tiles;
+    // TC_MODE_GELU_ROWS: row gate_ids[m] of gate_rows ([rows, gate_ld] bf16), columns from gate_col0
+    const int* gate_ids;
+    const bf16* gate_rows;
+    int64_t gate_ld;
+    int gate_col0;
 };
 
 // A load that the compiler leaves where it is written (it may not sink it below a barrier to the
@@ -306,11 +312,15 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         for (int q = 1; q < 8; ++q) acc += v[q];
         return acc;
     };
-    if (p.mode == TC_MODE_PLAIN || p.mode == TC_MODE_RELU2 || p.mode == TC_MODE_TANH) {
+    if (p.mode == TC_MODE_PLAIN || p.mode == TC_MODE_RELU2 || p.mode == TC_MODE_TANH || p.mode == TC_MODE_GELU_ROWS) {
         for (int i = 0, m = rank; m < m_valid; ++i, m += csize) {
             float val = tile_sum(i, col) * inv_s[m];
             if (p.mode == TC_MODE_RELU2) { val = fmaxf(val, 0.f); val *= val; }
             if (p.mode == TC_MODE_TANH) val = tanhf(val);
+            if (p.mode == TC_MODE_GELU_ROWS && n_ok) {
+                const float e = __bfloat162float(p.gate_rows[(int64_t)p.gate_ids[m0 + m] * p.gate_ld + p.gate_col0 + n0 + col]);
+                val = 0.5f * val * (1.f + tanhf(0.7978845608028654f * (val + 0.044715f * val * val * val))) * e;
+            }
             if (n_ok) {
                 const int64_t o = (int64_t)(m0 + m) * p.ldo + n0 + col;
                 if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = val;
@@ -466,7 +476,8 @@ static int run_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, TcPara
     const int M = p.M, N = p.N, K = p.K;
     if (!acorn_gemm_tc_supported(M, N, K, ldx, ldw) || splits < 1 || splits > 8) return ACORN_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACORN_ERR_UNSUPPORTED;
-    if (p.mode != TC_MODE_PLAIN && p.mode != TC_MODE_RELU2 && p.mode != TC_MODE_TANH && (M > 64 || p.out_f32))
+    if (p.mode != TC_MODE_PLAIN && p.mode != TC_MODE_RELU2 && p.mode != TC_MODE_TANH && p.mode != TC_MODE_GELU_ROWS &&
+        (M > 64 || p.out_f32))
         return ACORN_ERR_UNSUPPORTED;
     if (p.ss_in != nullptr && (M > 64 || p.ss_parts < 1 || p.norm_width < 1)) return ACORN_ERR_UNSUPPORTED;
     p.kblocks = (K + TC_BK - 1) / TC_BK;
@@ -503,6 +514,18 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
     p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;
     p.mode = mode; p.ss_in = ss_in; p.ss_parts = ss_parts; p.norm_width = norm_width; p.eps = eps;
     p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.ss_out = ss_out;
+    return run_tc(x, ldx, w, ldw, p, splits, per_sm, stream);
+}
+
+// out[m, n] = gelu_tanh((x w^T)[m, n]) * rows[ids[m], col0 + n] (TC_MODE_GELU_ROWS): rows [any, ld_rows] bf16.
+extern "C" int acorn_gemm_tc_gelu_rows(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
+                                       int N, int K, int splits, int per_sm, const int* ids, const void* rows,
+                                       int64_t ld_rows, int col0, cudaStream_t stream) {
+    if (ids == nullptr || rows == nullptr || col0 < 0) return ACORN_ERR_UNSUPPORTED;
+    TcParams p = {};
+    p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.out_f32 = 0;
+    p.mode = TC_MODE_GELU_ROWS;
+    p.gate_ids = ids; p.gate_rows = (const bf16*)rows; p.gate_ld = ld_rows; p.gate_col0 = col0;
     return run_tc(x, ldx, w, ldw, p, splits, per_sm, stream);
 }
 

@@ -176,6 +176,8 @@ class _Sigs:
     acorn_attention_tc_error = []
     acorn_gemm_tc_ex = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                         c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
+    acorn_gemm_tc_gelu_rows = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p, c_void_p, c_int64, c_int, c_void_p]
     acorn_gemm_tc_qkv_rope = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                               c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
@@ -1342,16 +1344,17 @@ def conv_state_update(main: torch.Tensor, state: torch.Tensor, conv_off: int, ro
 
 DELTA_MIN_SEGMENT = 64              # tokens: shorter segments are not worth a second pass
 DELTA_MAX_SEGMENTS = 16
-DELTA_ENOUGH_BLOCKS = 600           # blocks of 256 threads that keep the device busy
+DELTA_WAVE_BLOCKS = 296             # blocks of the segmented passes that run at once (148 SMs x 2: their shared memory)
 
 
 def delta_segments(longest_row: int, num_rows: int, heads: int, dim: int, vdim: int) -> tuple[int, int]:
     """(tokens a segment, segments a row) for the form of ``delta_rule`` that reads the state first; (0, 1): rows in
     one piece.  Rows run side by side with heads and tiles of columns; where those are too few to fill the device
-    and a row is long, rows are cut into segments that run side by side, at the price of a second pass."""
-    cols = 256 // (4 if dim <= 32 else 8 if dim <= 128 else 16)         # columns a block of the segmented passes takes
+    and a row is long, rows are cut into segments that run side by side, at the price of a second pass: as many
+    as still run at once (a second wave of blocks would wait for the first)."""
+    cols = 64 if dim <= 128 else 16                                     # columns a block of the segmented passes takes
     blocks = num_rows * heads * -(-vdim // cols)
-    nseg = min(DELTA_MAX_SEGMENTS, longest_row // DELTA_MIN_SEGMENT, -(-DELTA_ENOUGH_BLOCKS // blocks))
+    nseg = min(DELTA_MAX_SEGMENTS, longest_row // DELTA_MIN_SEGMENT, DELTA_WAVE_BLOCKS // max(blocks, 1))
     if nseg < 2:
         return 0, 1
     return -(-longest_row // nseg), nseg
@@ -1478,6 +1481,27 @@ def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
     out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     _ok(lib().acorn_activation(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], ACTIVATIONS[kind],
                                dtype_code(x.dtype), _stream()), "activation")
+    return out
+
+
+def side_gate_linear(x: torch.Tensor, w: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, col0: int) -> torch.Tensor:
+    """``gelu_tanh(x w^T)[t] * table[token_ids[t], col0 : col0 + n]`` for x [T, K], w [n, K]: the gate as the epilogue
+    of the one-CTA tcgen05 product where that runs (bfloat16, at most GEMM_TC_MAX_ROWS rows: the product is not
+    rounded before the gate), else the product followed by ``side_gate``."""
+    _check(table, "table", x.dtype, 2)
+    _check(token_ids, "token_ids", torch.int32, 1)
+    T, n = x.shape[0], w.shape[0]
+    if table.stride(1) != 1 or col0 < 0 or col0 + n > table.shape[1] or token_ids.numel() != T:
+        raise KernelError(f"side_gate_linear: x {tuple(x.shape)} / w {tuple(w.shape)} / table {tuple(table.shape)} / "
+                          f"first column {col0} do not fit")
+    if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T <= GEMM_TC_MAX_ROWS and gemm_tc_supported(x, w)):
+        return side_gate(linear(x, w, out_dtype=x.dtype), token_ids, table, col0)
+    K = x.shape[1]
+    splits, per_sm = gemm_tc_plan(T, n, K, device_sms(x.device))
+    out = torch.empty((T, n), dtype=torch.bfloat16, device=x.device)
+    _ok(lib().acorn_gemm_tc_gelu_rows(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+                                      T, n, K, int(splits), int(per_sm), token_ids.data_ptr(), table.data_ptr(),
+                                      table.stride(0), int(col0), _stream()), "gemm_tc_side_gate", f"{T}x{n}x{K}")
     return out
 
 

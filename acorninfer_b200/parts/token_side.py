@@ -47,8 +47,7 @@ class TokenSide(LayerExtra):
         """``defer``: the normed sum is not taken here but handed back (``ops.NormedPending``) for the kernel of
         the norm that follows."""
         dt = self.ctx.dtype
-        z = ops.linear(rows, self.w_gate, out_dtype=dt)
-        g = ops.side_gate(z, inputs.token_ids, self.table, self.index * self.dim)
+        g = ops.side_gate_linear(rows, self.w_gate, inputs.token_ids, self.table, self.index * self.dim)
         y = ops.linear(g, self.w_proj, out_dtype=dt)
         pending = ops.NormedPending(y, self.norm32, self.eps)
         if defer:

@@ -530,6 +530,15 @@ def test_activations_side_rows_norm_pairs_and_the_recurrence_inputs(dtype, tol):
     z = torch.randn(T, 5, generator=g).to(dtype)
     got = o.side_gate(z.to(DEV), ids.to(DEV), table.to(DEV), 11).double().cpu()
     assert (got - plain.gelu_tanh(z.double()) * table[ids.long()][:, 11:16].double()).abs().max() < tol * 4
+    # the same with the gate's product in front: as the epilogue of the tensor-core product (bfloat16, few rows), or as
+    # product and gate kernel (float32; many rows; a width the tensor-core product does not take)
+    for rows, K, n in ((T, 48, 5), (3, 64, 12), (300, 48, 5), (T, 44, 5)):
+        xs = torch.randn(rows, K, generator=g).to(dtype)
+        wg = (torch.randn(n, K, generator=g) / math.sqrt(K)).to(dtype)
+        ids2 = torch.randint(0, 50, (rows,), generator=g, dtype=torch.int32)
+        got = o.side_gate_linear(xs.to(DEV), wg.to(DEV), ids2.to(DEV), table.to(DEV).contiguous(), 17 - n).double().cpu()
+        want = plain.gelu_tanh(xs.double() @ wg.double().T) * table[ids2.long()][:, 17 - n:17].double()
+        assert (got - want).abs().max() < tol * 6, (rows, K, n)
     # a sublayer's output norm added to the stream, and the next sublayer's input norm of the sum
     resid = torch.randn(T, W, generator=g) * 3
     y = torch.randn(T, W, generator=g).to(dtype)
