@@ -655,6 +655,8 @@ def design_bench(args) -> int:
            "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "impl": "ours", "n_gpus": 1, "steps": args.steps,
            "warmup": args.warmup, "peaks": pk, "sizes": {}}
     context, prompt = 2048, 2048
+    clocks = ClockSampler()
+    clocks.start()
     for name in (args.design_sizes.split(",") if args.design_sizes else list(KOGONEX_SIZES)):
         models = design_models(design, name)
         res = {}
@@ -695,6 +697,7 @@ def design_bench(args) -> int:
             torch.cuda.empty_cache()
         out["sizes"][name] = res
     out["value"] = out["sizes"][next(iter(out["sizes"]))][design]["decode_b8_tok_s"]
+    out["clocks"] = clocks.stop()
     print(json.dumps(out))
     return 0
 
