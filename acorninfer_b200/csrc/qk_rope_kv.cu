@@ -243,6 +243,143 @@ static int launch_rope_vec(T* qkv, const float* q_w, const float* k_w, const flo
                                         table_stride, k_pages, v_pages, tokens, nq, nkv, P, eps, write_kv, stream);
 }
 
+// Bias, convolution over time, norm and cache write for heads that are not rotated, four channels a lane
+// (8- or 16-byte accesses): LPH lanes a head (a power of two, at most 32, 4 LPH >= the wider of d and dv),
+// a lane's weights of all taps in registers (TAPS of them, 0: no convolution), the taps in the order of the
+// general kernel.  A lane walks tpt consecutive tokens of the step and carries the inputs before the current
+// token along in registers while it stays within a row (a row's first token reads them from the request's
+// memory).  Widths, row strides and state offsets are multiples of four.
+template <typename T, int TAPS>
+__global__ void qk_conv_kv_vec_kernel(T* __restrict__ qkv, const float* __restrict__ q_w,
+                                      const float* __restrict__ k_w, const int* __restrict__ positions,
+                                      const int* __restrict__ token_row, const int* __restrict__ block_table,
+                                      const int* __restrict__ page_base, int table_stride, T* __restrict__ k_pages,
+                                      T* __restrict__ v_pages, int tokens, int nq, int nkv, int d, int dv, int P,
+                                      float eps, int write_kv, int64_t ld, QkConv cv, T* __restrict__ q_out,
+                                      int64_t ld_q, int lph_log2, int tpt) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int PAST = TAPS > 1 ? TAPS - 1 : 1;
+    const int heads = write_kv ? (nq + 2 * nkv) : nq;
+    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t item = gid >> lph_log2;
+    const int l = (int)(gid & ((1 << lph_log2) - 1));
+    const int64_t chunks = ((int64_t)tokens + tpt - 1) / tpt;
+    const bool in_range = item < chunks * heads;
+    const int64_t it = in_range ? item : 0;
+    const int64_t t_first = (it / heads) * tpt;
+    const int h = (int)(it % heads);
+    const bool is_v = h >= nq + nkv;
+    const bool lane_on = in_range && 4 * l < (is_v ? dv : d);
+    const int64_t chan = (is_v ? (int64_t)(nq + nkv) * d + (int64_t)(h - nq - nkv) * dv : (int64_t)h * d) + 4 * l;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 b = zero, g = zero;
+    const float* nw = is_v ? nullptr : (h < nq ? q_w : k_w);
+    float w[TAPS > 0 ? 4 * TAPS : 1];                                     // w[i * TAPS + j]: channel i of the lane, tap j
+    if (lane_on) {
+        if (cv.bias) b = *reinterpret_cast<const float4*>(cv.bias + chan);
+        if (nw) g = *reinterpret_cast<const float4*>(nw + 4 * l);
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            const float4 v = *reinterpret_cast<const float4*>(cv.w + chan * TAPS + 4 * j);
+            w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+        }
+    }
+    float4 past[PAST];                                                    // the inputs before the current token, oldest first
+    float4 before = zero;                                                 // the token before's own input
+    for (int k = 0; k < tpt; ++k) {
+        const int64_t t = t_first + k;
+        const bool active = lane_on && t < tokens;
+        float4 x = zero;
+        int r = 0;
+        if (active) {
+            T* src = qkv + t * ld + chan;
+            const float4 raw = Vec4<T>::load(src);
+            const float4 own = make_float4(raw.x + b.x, raw.y + b.y, raw.z + b.z, raw.w + b.w);
+            r = token_row[t];
+            if constexpr (TAPS == 0) {
+                x = own;
+            } else {
+                if constexpr (TAPS > 1) {
+                    const int i0 = (int)t - cv.row_start[r];              // the token's index within its row
+                    if (k == 0 || i0 == 0) {
+                        float* cstate = cv.state + (int64_t)cv.row_slot[r] * cv.slot_stride + cv.conv_off + chan;
+                        const bool shift = cv.update_single && cv.row_start[r + 1] - cv.row_start[r] == 1;
+#pragma unroll
+                        for (int j = 0; j < TAPS - 1; ++j) {
+                            const int idx = i0 - (TAPS - 1) + j;          // negative: before the step
+                            if (idx >= 0) {
+                                const float4 u = Vec4<T>::load(src + (int64_t)(idx - i0) * ld);
+                                past[j] = make_float4(u.x + b.x, u.y + b.y, u.z + b.z, u.w + b.w);
+                            } else {
+                                past[j] = *reinterpret_cast<const float4*>(cstate + (int64_t)(TAPS - 1 + idx) * cv.channels);
+                            }
+                            // the row's only token: a lane alone reads and writes its channels, oldest entry first
+                            if (shift && j > 0) *reinterpret_cast<float4*>(cstate + (int64_t)(j - 1) * cv.channels) = past[j];
+                        }
+                        if (shift) *reinterpret_cast<float4*>(cstate + (int64_t)(TAPS - 2) * cv.channels) = own;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < TAPS - 2; ++j) past[j] = past[j + 1];
+                        past[TAPS - 2] = before;
+                    }
+#pragma unroll
+                    for (int j = 0; j < TAPS - 1; ++j) {
+                        x.x = fmaf(w[j], past[j].x, x.x);
+                        x.y = fmaf(w[TAPS + j], past[j].y, x.y);
+                        x.z = fmaf(w[2 * TAPS + j], past[j].z, x.z);
+                        x.w = fmaf(w[3 * TAPS + j], past[j].w, x.w);
+                    }
+                }
+                x.x = fmaf(w[TAPS - 1], own.x, x.x);
+                x.y = fmaf(w[2 * TAPS - 1], own.y, x.y);
+                x.z = fmaf(w[3 * TAPS - 1], own.z, x.z);
+                x.w = fmaf(w[4 * TAPS - 1], own.w, x.w);
+            }
+            before = own;
+        }
+        // every lane of the warp takes part in the sums, whatever its head is
+        float ss = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        for (int o = (1 << lph_log2) >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (active) {
+            if (nw) {
+                const float inv = rsqrtf(ss / (float)d + eps);
+                x = make_float4(x.x * inv * g.x, x.y * inv * g.y, x.z * inv * g.z, x.w * inv * g.w);
+            }
+            T* dst;
+            if (h < nq) {
+                dst = q_out ? q_out + t * ld_q + chan : qkv + t * ld + chan;
+            } else {
+                const int pos = positions[t];
+                const int kvh = (h - nq) % nkv;
+                const int page = block_table[(int64_t)r * table_stride + (pos / P - page_base[r])];
+                const int64_t slot = ((int64_t)page * nkv + kvh) * P + (pos % P);
+                dst = (is_v ? v_pages + slot * dv : k_pages + slot * d) + 4 * l;
+            }
+            Vec4<T>::store(dst, x);
+        }
+    }
+}
+
+template <typename T, int TAPS>
+static int launch_conv_vec(T* qkv, const float* q_w, const float* k_w, const int* positions, const int* token_row,
+                           const int* block_table, const int* page_base, int table_stride, T* k_pages, T* v_pages,
+                           int tokens, int nq, int nkv, int d, int dv, int P, float eps, int write_kv, int64_t ld,
+                           const QkConv& cv, T* q_out, int64_t ld_q, cudaStream_t stream) {
+    const int widest = (write_kv && dv > d) ? dv : d;
+    int lph_log2 = 0;
+    while ((4 << lph_log2) < widest) ++lph_log2;
+    const int heads = write_kv ? (nq + 2 * nkv) : nq;
+    const int tpt = tokens > 1024 ? 8 : (tokens > 256 ? 4 : 1);                // a step of few tokens: a lane a token
+    const int64_t threads = (((int64_t)tokens + tpt - 1) / tpt * heads) << lph_log2;
+    const int block = threads >= 256 ? 256 : 128;
+    return acorn_launch(qk_conv_kv_vec_kernel<T, TAPS>, dim3((unsigned)((threads + block - 1) / block)), dim3(block), 0,
+                        stream, qkv, q_w, k_w, positions, token_row, block_table, page_base, table_stride, k_pages,
+                        v_pages, tokens, nq, nkv, d, dv, P, eps, write_kv, ld, cv, q_out, ld_q, lph_log2, tpt);
+}
+
+static bool qk_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, const float* inv_freq,
                                 const int* positions, const int* token_row, const int* block_table,
                                 const int* page_base, int table_stride, void* k_pages, void* v_pages,
@@ -276,6 +413,25 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
             default: ROPE_VEC(32); break;
         }
 #undef ROPE_VEC
+    }
+    const int vec_taps = conv_w ? taps : 0;
+    if (!plain_rows && rot == 0 && !v_from_k && vec_taps <= 4 && d % 4 == 0 && dv % 4 == 0 && d <= 128 && dv <= 128 &&
+        ld % 4 == 0 && ld_q % 4 == 0 && slot_stride % 4 == 0 && conv_off % 4 == 0 && qk_aligned16(qkv) &&
+        qk_aligned16(q_out) && qk_aligned16(k_pages) && qk_aligned16(v_pages) && qk_aligned16(q_w) &&
+        qk_aligned16(k_w) && qk_aligned16(conv_w) && qk_aligned16(bias) && qk_aligned16(state)) {
+#define CONV_VEC(TAPS)                                                                                                \
+    ACORN_DISPATCH_DTYPE(dtype, T, return (launch_conv_vec<T, TAPS>((T*)qkv, q_w, k_w, positions, token_row,           \
+                                                                     block_table, page_base, table_stride, (T*)k_pages, \
+                                                                     (T*)v_pages, tokens, nq, nkv, d, dv, P, eps,       \
+                                                                     write_kv, ld, cv, (T*)q_out, ld_q, stream)))
+        switch (vec_taps) {
+            case 0: CONV_VEC(0); break;
+            case 1: CONV_VEC(1); break;
+            case 2: CONV_VEC(2); break;
+            case 3: CONV_VEC(3); break;
+            default: CONV_VEC(4); break;
+        }
+#undef CONV_VEC
     }
     const int warps = 4;
     const int heads = write_kv ? (nq + 2 * nkv) : nq;

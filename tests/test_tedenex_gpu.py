@@ -432,22 +432,27 @@ def test_recurrence_that_reads_the_state_first_across_steps_and_slots(H, dim, lo
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-def test_blends_with_the_row_before_carry_it_between_steps(dtype, tol):
+@pytest.mark.parametrize("W,off,tail,single", [(20, 7, 3, False), (20, 8, 4, False), (20, 8, 4, True), (520, 4, 0, True),
+                                               (22, 8, 2, True)])
+def test_blends_with_the_row_before_carry_it_between_steps(dtype, tol, W, off, tail, single):
+    """Widths, offsets and slot sizes that are and are not multiples of four (four channels a thread, or one);
+    the kept row written by the follow-up kernel, or by the blend kernel itself for rows of one token."""
     o = ops()
     g = torch.Generator().manual_seed(4)
-    W, n, off = 20, 5, 7
+    n = 5
     slots, cuts = [2, 0], ([4, 1], [1, 3], [6, 2])
     rows = [torch.randn(sum(c[r] for c in cuts), W, generator=g).to(dtype) for r in range(2)]
     mu = torch.rand(n, W, generator=g)
-    state = torch.zeros(4, off + W + 3, device=DEV)
+    state = torch.zeros(4, off + W + tail, device=DEV)
     i32 = dict(dtype=torch.int32, device=DEV)
     at = [0, 0]
     for lens in cuts:
         h = torch.cat([x[a:a + m] for x, a, m in zip(rows, at, lens)]).to(DEV)
         row_start = torch.tensor(np.cumsum([0] + lens), **i32)
         token_row = torch.tensor([r for r, m in enumerate(lens) for _ in range(m)], **i32)
-        out = o.token_shift(h, mu.to(DEV), state, off, token_row, row_start, torch.tensor(slots, **i32)).float().cpu()
-        o.conv_state_update(h, state, off, row_start, torch.tensor(slots, **i32), 2, W, 2)
+        out = o.token_shift(h, mu.to(DEV), state, off, token_row, row_start, torch.tensor(slots, **i32),
+                            update_single=single).float().cpu()
+        o.conv_state_update(h, state, off, row_start, torch.tensor(slots, **i32), 2, W, 2, skip_single=single)
         t0 = 0
         for r, m in enumerate(lens):
             x = rows[r].double()
@@ -457,29 +462,37 @@ def test_blends_with_the_row_before_carry_it_between_steps(dtype, tol):
             assert (out[:, t0:t0 + m].double() - want).abs().max() < tol
             t0 += m
             at[r] += m
-    assert float(state[:, :off].abs().max()) == 0.0 and float(state[:, off + W:].abs().max()) == 0.0
+    assert float(state[:, :off].abs().max()) == 0.0
+    assert tail == 0 or float(state[:, off + W:].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
-@pytest.mark.parametrize("taps,nq,nkv,d,dv", [(4, 4, 2, 12, 20), (1, 2, 2, 16, 16), (2, 3, 1, 64, 64), (None, 2, 1, 8, 6)])
-def test_bias_convolution_norm_and_cache_write_across_steps(dtype, tol, taps, nq, nkv, d, dv):
+@pytest.mark.parametrize("taps,nq,nkv,d,dv", [(4, 4, 2, 12, 20), (1, 2, 2, 16, 16), (2, 3, 1, 64, 64), (None, 2, 1, 8, 6),
+                                              (3, 2, 1, 24, 40), (None, 2, 2, 32, 8), (5, 2, 1, 16, 16), (4, 3, 3, 128, 128)])
+@pytest.mark.parametrize("pad,single,long", [(3, False, False), (8, False, False), (8, True, False), (8, True, True)])
+def test_bias_convolution_norm_and_cache_write_across_steps(dtype, tol, taps, nq, nkv, d, dv, pad, single, long):
     """The projected rows of two requests in three steps: bias, convolution over time (its memory in the state
     slot between steps, zeros before a request's start), q/k norm; queries into their own buffer, keys and
-    values into pages."""
+    values into pages.  Rows and state slots whose sizes are and are not multiples of four (four channels a lane,
+    or one); the memory moved on by the follow-up kernel, or for rows of one token by the convolving kernel; steps of
+    hundreds of tokens (a lane then walks several tokens, also across the border of two rows)."""
     o = ops()
     g = torch.Generator().manual_seed(d)
     P, eps = 4, 1e-5
     C = (nq + nkv) * d + nkv * dv
     cuts, slots = ([5, 1], [1, 2], [7, 3]), [1, 3]
+    if long:
+        cuts = ([290, 1], [1, 331], [3, 1201], [1, 1])
+    pages = 12 if not long else 800
     totals = [sum(c[r] for c in cuts) for r in range(2)]
-    proj = [torch.randn(T, C + 3, generator=g).to(dtype) for T in totals]              # rows wider than the channels
+    proj = [torch.randn(T, C + pad, generator=g).to(dtype) for T in totals]            # rows wider than the channels
     bias = torch.randn(C, generator=g)
     w = None if taps is None else torch.randn(C, taps, generator=g) * 0.5
     qw, kw = torch.rand(d, generator=g) + 0.5, torch.rand(d, generator=g) + 0.5
-    lay = rows_layout([0, 0], totals, P, 12, seed=1)
-    k_pages = torch.zeros(12, nkv, P, d, dtype=dtype, device=DEV)
-    v_pages = torch.zeros(12, nkv, P, dv, dtype=dtype, device=DEV)
-    state = torch.zeros(5, max(((taps or 1) - 1) * C, 1) + 2, device=DEV)
+    lay = rows_layout([0, 0], totals, P, pages, seed=1)
+    k_pages = torch.zeros(pages, nkv, P, d, dtype=dtype, device=DEV)
+    v_pages = torch.zeros(pages, nkv, P, dv, dtype=dtype, device=DEV)
+    state = torch.zeros(5, max(((taps or 1) - 1) * C, 1) + (2 if pad == 3 else 4 - max(((taps or 1) - 1) * C, 1) % 4), device=DEV)
     i32 = dict(dtype=torch.int32, device=DEV)
     at = [0, 0]
     got_q = [[], []]
@@ -489,12 +502,14 @@ def test_bias_convolution_norm_and_cache_write_across_steps(dtype, tol, taps, nq
         token_row = torch.tensor([r for r, m in enumerate(lens) for _ in range(m)], **i32)
         positions = torch.tensor([a + i for a, m in zip(at, lens) for i in range(m)], **i32)
         q_out = torch.zeros(sum(lens), nq * d + 8, dtype=dtype, device=DEV)
-        conv = None if taps is None else o.ShortConv(w.to(DEV), state, 0, row_start, torch.tensor(slots, **i32))
+        conv = None if taps is None else o.ShortConv(w.to(DEV), state, 0, row_start, torch.tensor(slots, **i32),
+                                                     update_single=single)
         o.qk_rope_kv(rows, qw.to(DEV), kw.to(DEV), torch.zeros(0, device=DEV), positions, token_row, lay["block_table"],
                      lay["page_base"], k_pages, v_pages, nq, nkv, d, 0, False, eps, value_dim=dv, bias32=bias.to(DEV),
                      conv=conv, q_out=q_out)
         if taps is not None and taps > 1:
-            o.conv_state_update(rows, state, 0, row_start, torch.tensor(slots, **i32), 2, C, taps, bias32=bias.to(DEV))
+            o.conv_state_update(rows, state, 0, row_start, torch.tensor(slots, **i32), 2, C, taps, skip_single=single,
+                                bias32=bias.to(DEV))
         assert float(q_out[:, nq * d:].abs().max()) == 0.0
         t0 = 0
         for r, m in enumerate(lens):
