@@ -407,9 +407,85 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ resid32, const T* __restr
     }
 }
 
+// Both of the above, four entries a thread and access (8 or 16 bytes), a thread's part of the row in registers
+// (NV vectors) from the first read to the last write: widths that are multiples of four, up to 16 NV threads.
+// NEXT: the second norm follows (`out` is then the normed row, else the rounded new residual or null).
+template <typename T, int NV, bool NEXT>
+__global__ void rmsnorm_add_vec_kernel(float* __restrict__ resid32, const T* __restrict__ y, const float* __restrict__ w,
+                                       const float* __restrict__ w_next, T* __restrict__ out, int H, float eps,
+                                       float eps_next) {
+    __shared__ float scratch[32];
+    pdl_wait();
+    pdl_trigger();
+    const int64_t row = blockIdx.x;
+    const int n4 = H >> 2;
+    const T* yr = y + row * H;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        v[k] = i < n4 ? Vec4<T>::load(yr + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    float* x = resid32 + row * H;
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n4) {
+            const float4 r = *reinterpret_cast<const float4*>(x + 4 * i);
+            const float4 g = *reinterpret_cast<const float4*>(w + 4 * i);
+            v[k] = make_float4(r.x + v[k].x * inv * g.x, r.y + v[k].y * inv * g.y, r.z + v[k].z * inv * g.z,
+                               r.w + v[k].w * inv * g.w);
+            *reinterpret_cast<float4*>(x + 4 * i) = v[k];
+            if (!NEXT && out) Vec4<T>::store(out + row * H + 4 * i, v[k]);
+            s2 += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    if (!NEXT) return;
+    s2 = block_sum(s2, scratch);
+    const float inv2 = rsqrtf(s2 / (float)H + eps_next);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n4) {
+            const float4 g = *reinterpret_cast<const float4*>(w_next + 4 * i);
+            Vec4<T>::store(out + row * H + 4 * i,
+                           make_float4(v[k].x * inv2 * g.x, v[k].y * inv2 * g.y, v[k].z * inv2 * g.z, v[k].w * inv2 * g.w));
+        }
+    }
+}
+
+// 0: launched; -1: not a case of the vector form
+template <bool NEXT>
+static int launch_rmsnorm_add_vec(float* resid32, const void* y, const float* w, const float* w_next, void* out, int rows,
+                                  int H, float eps, float eps_next, int dtype, cudaStream_t stream, int* status) {
+    const uintptr_t all = (uintptr_t)resid32 | (uintptr_t)y | (uintptr_t)w | (uintptr_t)w_next | (uintptr_t)out;
+    if (H % 4 != 0 || (all & 15) != 0) return -1;
+    const int n4 = H / 4;
+    const int threads = n4 <= 256 ? (n4 + 31) / 32 * 32 : (n4 <= 1024 ? 256 : 512);
+    const int nv = (n4 + threads - 1) / threads;
+    if (nv > 4) return -1;
+#define NORM_VEC(NV)                                                                                                   \
+    ACORN_DISPATCH_DTYPE(dtype, T, *status = acorn_launch(rmsnorm_add_vec_kernel<T, NV, NEXT>, dim3(rows), dim3(threads), \
+                                                          0, stream, resid32, (const T*)y, w, w_next, (T*)out, H, eps,  \
+                                                          eps_next))
+    if (nv == 1) NORM_VEC(1);
+    else if (nv == 2) NORM_VEC(2);
+    else NORM_VEC(4);
+#undef NORM_VEC
+    return 0;
+}
+
 extern "C" int acorn_rmsnorm_add(float* resid32, const void* y, const float* w, void* rounded, int rows, int H,
                                  float eps, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    int status = 0;
+    if (launch_rmsnorm_add_vec<false>(resid32, y, w, nullptr, rounded, rows, H, eps, 0.f, dtype, stream, &status) == 0)
+        return status;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(rmsnorm_add_kernel<T>, dim3(rows), dim3(threads), 0, stream, resid32,
                                                        (const T*)y, w, (T*)rounded, H, eps));
@@ -454,6 +530,9 @@ __global__ void rmsnorm_add_norm_kernel(float* __restrict__ resid32, const T* __
 extern "C" int acorn_rmsnorm_add_norm(float* resid32, const void* y, const float* w, const float* w_next, void* normed,
                                       int rows, int H, float eps, float eps_next, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    int status = 0;
+    if (launch_rmsnorm_add_vec<true>(resid32, y, w, w_next, normed, rows, H, eps, eps_next, dtype, stream, &status) == 0)
+        return status;
     if ((size_t)H * sizeof(float) > 48 * 1024) return ACORN_ERR_UNSUPPORTED;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(rmsnorm_add_norm_kernel<T>, dim3(rows), dim3(threads),

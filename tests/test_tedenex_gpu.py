@@ -555,14 +555,20 @@ def test_activations_side_rows_norm_pairs_and_the_recurrence_inputs(dtype, tol):
         want = plain.gelu_tanh(xs.double() @ wg.double().T) * table[ids2.long()][:, 17 - n:17].double()
         assert (got - want).abs().max() < tol * 6, (rows, K, n)
     # a sublayer's output norm added to the stream, and the next sublayer's input norm of the sum
-    resid = torch.randn(T, W, generator=g) * 3
-    y = torch.randn(T, W, generator=g).to(dtype)
-    w1, w2 = torch.rand(W, generator=g) + 0.5, torch.rand(W, generator=g) + 0.5
-    stream = resid.clone().to(DEV)
-    normed = o.rmsnorm_add_norm(stream, y.to(DEV), w1.to(DEV), 1e-5, w2.to(DEV), 1e-6).double().cpu()
-    s = resid.double() + plain.norm_plain(y.double(), w1.double(), 1e-5)
-    assert (stream.cpu().double() - s).abs().max() < 1e-5
-    assert (normed - plain.norm_plain(s, w2.double(), 1e-6)).abs().max() < tol * 4
+    # (widths that are no multiple of four: an entry a thread; the others four, with 1, 2 or 4 such parts a thread)
+    for Wn in (W, 62, 4, 1000, 1028, 2048, 2052, 4100, 8192, 8196):
+        resid = torch.randn(T, Wn, generator=g) * 3
+        y = torch.randn(T, Wn, generator=g).to(dtype)
+        w1, w2 = torch.rand(Wn, generator=g) + 0.5, torch.rand(Wn, generator=g) + 0.5
+        stream = resid.clone().to(DEV)
+        normed = o.rmsnorm_add_norm(stream, y.to(DEV), w1.to(DEV), 1e-5, w2.to(DEV), 1e-6).double().cpu()
+        s = resid.double() + plain.norm_plain(y.double(), w1.double(), 1e-5)
+        assert (stream.cpu().double() - s).abs().max() < 1e-5, Wn
+        assert (normed - plain.norm_plain(s, w2.double(), 1e-6)).abs().max() < tol * 4, Wn
+        stream = resid.clone().to(DEV)
+        rounded = o.rmsnorm_add(stream, y.to(DEV), w1.to(DEV), 1e-5)
+        assert (stream.cpu().double() - s).abs().max() < 1e-5, Wn
+        assert rounded is None if dtype == torch.float32 else torch.equal(rounded.float().cpu(), stream.cpu().to(dtype).float()), Wn
     # the recurrence's inputs: float32 copies, decay = exp(-exp(z + w0)), gate = silu(g)
     H, d = 3, 10
     r, k, v, gg = (torch.randn(T, H * d, generator=g).to(dtype) for _ in range(4))
