@@ -769,6 +769,223 @@ class TedenexConfig(ModelConfig):
 _TEDENEX_MIXERS = {"attention": ConvAttentionConfig, "wkv": TimeMixConfig, "latent_attention": LatentAttentionConfig}
 
 
+# --------------------------------------------------------------------------- Zigolix
+
+
+@dataclass(frozen=True)
+class SinkAttentionConfig:
+    """Grouped-query attention whose values are the keys as projected; a part of each head rotated
+    (neighbouring pairs, optionally with stretched frequencies); q and k brought to unit root mean square
+    after the rotation; a sliding window; a learned sink per head in the softmax denominator."""
+
+    kind: ClassVar[str] = "attention"
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    mask_size: int | None = None
+    rot_dims: int = 0
+    rot_base: float = 10000.0
+    scaling: RotaryScaling | None = None
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "SinkAttentionConfig":
+        mask = _sub(m, "mask", where, required=False)
+        rot = _sub(m, "rot", where, required=False)
+        sc = None if rot is None else _sub(rot, "scaling", where + "rot.", required=False)
+        return cls(heads=_take(m, "heads", int), kv_heads=_take(m, "kv_heads", int), dim=_take(m, "dim", int),
+                   vdim=_take(m, "vdim", int), scale=_take(m, "scale", float),
+                   mask_size=None if mask is None else _take(mask, "size", int, None),
+                   rot_dims=0 if rot is None else _take(rot, "dims", int), rot_base=1e4 if rot is None else _take(rot, "base", float),
+                   scaling=None if sc is None else RotaryScaling(_take(sc, "factor", float), _take(sc, "original", int),
+                                                                 _take(sc, "fast", float), _take(sc, "slow", float)))
+
+    def check(self, where: str) -> None:
+        if min(self.heads, self.kv_heads, self.dim) < 1 or self.heads % self.kv_heads:
+            raise ConfigError(f"config.json: {where}sizes must be >= 1 and 'heads' a multiple of 'kv_heads'")
+        if self.vdim != self.dim:
+            raise ConfigError(f"config.json: {where}vdim must equal dim (the values are the keys), got {self.vdim} and {self.dim}")
+        if self.rot_dims % 2 or not (0 <= self.rot_dims <= self.dim):
+            raise ConfigError(f"config.json: {where}rot.dims must be even and at most dim, got {self.rot_dims}")
+        if self.mask_size is not None and self.mask_size < 1:
+            raise ConfigError(f"config.json: {where}mask.size must be >= 1, got {self.mask_size}")
+
+    def to_dict(self) -> dict:
+        out: dict = {"dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "scale": self.scale, "vdim": self.vdim}
+        if self.mask_size is not None:
+            out["mask"] = {"size": self.mask_size}
+        if self.rot_dims:
+            out["rot"] = {"base": self.rot_base, "dims": self.rot_dims}
+            if self.scaling is not None:
+                out["rot"]["scaling"] = asdict(self.scaling)
+        return out
+
+
+@dataclass(frozen=True)
+class DiffAttentionConfig:
+    """Differential attention: two score maps per head over the same values, combined as ``a1 - lambda a2``;
+    biased projections, no rotation, capped scores, a sliding window, a gate on the heads' outputs."""
+
+    kind: ClassVar[str] = "attention_2"
+    heads: int
+    kv_heads: int
+    dim: int                    # entries of ONE score map of a head (a query head holds two)
+    vdim: int
+    scale: float
+    diff: float
+    softcap: float | None = None
+    mask_size: int | None = None
+
+    @classmethod
+    def from_dict(cls, m: dict, where: str) -> "DiffAttentionConfig":
+        mask = _sub(m, "mask", where, required=False)
+        return cls(heads=_take(m, "heads", int), kv_heads=_take(m, "kv_heads", int), dim=_take(m, "dim", int),
+                   vdim=_take(m, "vdim", int), scale=_take(m, "scale", float), diff=_take(m, "diff", float),
+                   softcap=_take(m, "softcap", float, None),
+                   mask_size=None if mask is None else _take(mask, "size", int, None))
+
+    def check(self, where: str) -> None:
+        if min(self.heads, self.kv_heads, self.dim, self.vdim) < 1 or self.heads % self.kv_heads:
+            raise ConfigError(f"config.json: {where}sizes must be >= 1 and 'heads' a multiple of 'kv_heads'")
+        if self.softcap is not None and not self.softcap > 0:
+            raise ConfigError(f"config.json: {where}softcap must be > 0, got {self.softcap}")
+        if self.mask_size is not None and self.mask_size < 1:
+            raise ConfigError(f"config.json: {where}mask.size must be >= 1, got {self.mask_size}")
+
+    def to_dict(self) -> dict:
+        out: dict = {"diff": self.diff, "dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads,
+                     "scale": self.scale, "vdim": self.vdim}
+        if self.softcap is not None:
+            out["softcap"] = self.softcap
+        if self.mask_size is not None:
+            out["mask"] = {"size": self.mask_size}
+        return out
+
+
+@dataclass(frozen=True)
+class CappedExpertsConfig:
+    """A routed mixture of small experts of the capped form (``limit``), the chosen experts' softmax scores
+    divided by their sum, and optionally a shared expert of the same form that every token takes."""
+
+    ff: int
+    limit: float
+    experts: int
+    top: int
+    shared_ff: int | None = None
+    shared_limit: float | None = None
+
+    @classmethod
+    def from_dict(cls, f: dict, where: str) -> "CappedExpertsConfig":
+        e, r = _sub(f, "expert", where), _sub(f, "router", where)
+        sh = _sub(f, "shared", where, required=False)
+        return cls(ff=_take(e, "ff", int), limit=_take(e, "limit", float), experts=_take(r, "experts", int),
+                   top=_take(r, "top", int), shared_ff=None if sh is None else _take(sh, "ff", int),
+                   shared_limit=None if sh is None else _take(sh, "limit", float))
+
+    def check(self, where: str) -> None:
+        if self.ff < 1 or self.experts < 1 or not (1 <= self.top <= self.experts) or (self.shared_ff is not None and self.shared_ff < 1):
+            raise ConfigError(f"config.json: {where}sizes must be >= 1 and 1 <= router.top <= router.experts")
+        if not self.limit > 0 or (self.shared_limit is not None and not self.shared_limit > 0):
+            raise ConfigError(f"config.json: {where}'limit' must be > 0")
+
+    def to_dict(self) -> dict:
+        out: dict = {"expert": {"ff": self.ff, "limit": self.limit}, "kind": "moe",
+                     "router": {"experts": self.experts, "top": self.top}}
+        if self.shared_ff is not None:
+            out["shared"] = {"ff": self.shared_ff, "limit": self.shared_limit}
+        return out
+
+
+@dataclass(frozen=True)
+class ZigolixLayer:
+    type: str                                   # "attention" or "attention_2"
+    mixer: "SinkAttentionConfig | DiffAttentionConfig"
+    ff: "int | CappedExpertsConfig | None"      # inner width of the dense gated feed-forward; routed experts; none
+
+
+@dataclass(frozen=True)
+class ZigolixConfig(ModelConfig):
+    """Zigolix: pre-norm layers ``x += mixer(norm1(x)); x += ff(norm2(x))`` whose mixer is attention with a sink
+    and keys as values, or differential attention; the feed-forward is gated with the tanh form of gelu or a routed
+    mixture of capped experts beside a shared one.  A span of the layers may run several times in a row, each pass
+    with a cache of its own; every pass opens with ``x <- W_in [x; x0] + step[pass]`` (x0 the token rows).  A final
+    norm, an output matrix of its own and a factor on the logits.  ``config.json`` lists the layers in order."""
+
+    architecture: ClassVar[str] = "Zigolix"
+
+    vocab_size: int
+    hidden_size: int
+    norm_eps: float
+    layers: tuple[ZigolixLayer, ...]
+    loop: LayerLoop | None = None
+    logit_scale: float = 1.0
+    eos_token_id: tuple[int, ...] = field(default_factory=tuple)
+
+    def __post_init__(self) -> None:
+        if self.vocab_size < 1 or self.hidden_size < 1 or not self.layers:
+            raise ConfigError("config.json: 'vocab', 'width' must be >= 1 and 'layers' non-empty")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm 'eps' must be > 0, got {self.norm_eps}")
+        if self.loop is not None:
+            lp = self.loop
+            if not (0 <= lp.start < lp.stop <= len(self.layers)) or lp.times < 1:
+                raise ConfigError(f"config.json: loop must name layers start < stop <= {len(self.layers)} and times >= 1, "
+                                  f"got start {lp.start}, stop {lp.stop}, times {lp.times}")
+        for i, layer in enumerate(self.layers):
+            layer.mixer.check(f"layers[{i}].mixer.")
+            if isinstance(layer.ff, CappedExpertsConfig):
+                layer.ff.check(f"layers[{i}].mlp.")
+            elif layer.ff is not None and layer.ff < 1:
+                raise ConfigError(f"config.json: layers[{i}].mlp.ff must be >= 1, got {layer.ff}")
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "ZigolixConfig":
+        layers_raw = raw.get("layers")
+        if not isinstance(layers_raw, list) or not layers_raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, lr in enumerate(layers_raw):
+            where = f"layers[{i}]."
+            kind = lr.get("type") if isinstance(lr, dict) else None
+            if kind not in _ZIGOLIX_MIXERS:
+                raise ConfigError(f"config.json: {where}'type' must be one of {sorted(_ZIGOLIX_MIXERS)}, got {kind!r}")
+            mixer = _ZIGOLIX_MIXERS[kind].from_dict(_sub(lr, "mixer", where), where + "mixer.")
+            mlp = _sub(lr, "mlp", where, required=False)
+            if mlp is None:
+                ff = None
+            elif mlp.get("kind", "dense") == "dense":
+                ff = _take(mlp, "ff", int)
+            elif mlp.get("kind") == "moe":
+                ff = CappedExpertsConfig.from_dict(mlp, where + "mlp.")
+            else:
+                raise ConfigError(f"config.json: {where}mlp.kind must be 'dense' or 'moe', got {mlp.get('kind')!r}")
+            layers.append(ZigolixLayer(kind, mixer, ff))
+        loop = _sub(raw, "loop", "", required=False)
+        eos = raw.get("eos_token_id")
+        eos_ids = () if eos is None else tuple(int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos]))
+        return cls(vocab_size=_take(raw, "vocab", int), hidden_size=_take(raw, "width", int),
+                   norm_eps=_take(_sub(raw, "norm", ""), "eps", float), layers=tuple(layers),
+                   loop=None if loop is None else LayerLoop(_take(loop, "start", int), _take(loop, "stop", int),
+                                                            _take(loop, "times", int)),
+                   logit_scale=_take(raw, "logit_scale", float, 1.0), eos_token_id=eos_ids)
+
+    def to_dict(self) -> dict:
+        out: dict = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+                     "norm": {"eps": self.norm_eps}, "logit_scale": self.logit_scale}
+        out["layers"] = [{"type": l.type, "mixer": l.mixer.to_dict(),
+                          "mlp": None if l.ff is None else l.ff.to_dict() if isinstance(l.ff, CappedExpertsConfig)
+                          else {"ff": l.ff, "kind": "dense"}} for l in self.layers]
+        if self.loop is not None:
+            out["loop"] = {"start": self.loop.start, "stop": self.loop.stop, "times": self.loop.times}
+        if self.eos_token_id:
+            out["eos_token_id"] = list(self.eos_token_id)
+        return out
+
+
+_ZIGOLIX_MIXERS = {c.kind: c for c in (SinkAttentionConfig, DiffAttentionConfig)}
+
+
 def read_config_json(model_dir: str | Path) -> dict:
     path = Path(model_dir) / "config.json"
     if not path.is_file():

@@ -38,6 +38,9 @@ struct DecodeParams {
     AttnMask mask;           // attention_mask.cuh: window, blocks of positions, kept first keys
     float scale_log2;         // softmax scale * log2(e)
     const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
+    const float* sink;        // [nq] or null: exp(sink_h) in the softmax denominator (no key, no value; counted by split 0)
+    float scale, softcap;     // the plain scale; softcap c > 0: the scaled score becomes c tanh(score / c)
+    int maps;                 // score maps side by side in a head (1: the usual head; see attention_plain.cu)
 };
 
 template <int D>
@@ -77,7 +80,15 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int row = g + (i & 1) * 8, col = ks * 16 + 2 * tq + (i >> 1) * 8;
-                qa[ks][i] = row < rep ? *reinterpret_cast<const uint32_t*>(qrow + row * D + col) : 0u;
+                if (p.maps > 1) {
+                    // the (head, map) pair's query with zeros outside its map's entries of the key row
+                    const int dm = D / p.maps, hv = kvh * rep + row, a = hv % p.maps;
+                    qa[ks][i] = (row < rep && col / dm == a)
+                                    ? *reinterpret_cast<const uint32_t*>(p.q + (int64_t)t * p.q_stride + (int64_t)hv * dm + (col - a * dm))
+                                    : 0u;
+                } else {
+                    qa[ks][i] = row < rep ? *reinterpret_cast<const uint32_t*>(qrow + row * D + col) : 0u;
+                }
             }
         }
     }
@@ -128,8 +139,11 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int key = wkey0 + j * 8 + 2 * tq + (e & 1);
-                    s[j][e] = key < hi ? fmaf(s[j][e], p.scale_log2, -slope_log2[e >> 1] * (float)(pos - mask_key(key, vlo, lo)))
-                                       : -INFINITY;
+                    if (p.softcap > 0.f)
+                        s[j][e] = key < hi ? p.softcap * tanhf(s[j][e] * p.scale / p.softcap) * 1.4426950408889634f : -INFINITY;
+                    else
+                        s[j][e] = key < hi ? fmaf(s[j][e], p.scale_log2, -slope_log2[e >> 1] * (float)(pos - mask_key(key, vlo, lo)))
+                                           : -INFINITY;
                     mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
                 }
             float corr[2];
@@ -199,6 +213,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
             acc += sm_o[(w * 16 + h) * D + i] * f;
         }
         const int head = kvh * rep + h;
+        if (p.sink && split == 0) L += exp2f(p.sink[head] * 1.4426950408889634f - mstar);
         if (p.num_splits == 1) {
             p.out[((int64_t)t * p.nq + head) * D + i] = __float2bfloat16_rn(acc / L);
         } else {
@@ -276,13 +291,35 @@ extern "C" int acorn_attention_decode_supported(int nq, int nkv, int d) {
     return (d % 16 == 0 && d >= 16 && d <= 128) || d == 256;
 }
 
+extern "C" int acorn_attention_decode_ex(const void* q, int64_t q_stride, void* out, const void* k_pages,
+                                         const void* v_pages, const int* block_table, const int* page_base,
+                                         int table_stride, const int* token_row, const int* positions,
+                                         const int* token_list, int n, int nq, int nkv, int d, int P, float scale,
+                                         int window, int num_splits, float* part_o, float* part_lse,
+                                         int chunk, int keep, const float* slopes, const float* sink, float softcap,
+                                         int maps, cudaStream_t stream);
+
 extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out, const void* k_pages,
                                       const void* v_pages, const int* block_table, const int* page_base,
                                       int table_stride, const int* token_row, const int* positions,
                                       const int* token_list, int n, int nq, int nkv, int d, int P, float scale,
                                       int window, int num_splits, float* part_o, float* part_lse,
                                       int chunk, int keep, const float* slopes, cudaStream_t stream) {
+    return acorn_attention_decode_ex(q, q_stride, out, k_pages, v_pages, block_table, page_base, table_stride, token_row,
+                                     positions, token_list, n, nq, nkv, d, P, scale, window, num_splits, part_o, part_lse,
+                                     chunk, keep, slopes, nullptr, 0.f, 1, stream);
+}
+
+// The same with a sink per head, a cap on the scores and several score maps in a head.
+extern "C" int acorn_attention_decode_ex(const void* q, int64_t q_stride, void* out, const void* k_pages,
+                                         const void* v_pages, const int* block_table, const int* page_base,
+                                         int table_stride, const int* token_row, const int* positions,
+                                         const int* token_list, int n, int nq, int nkv, int d, int P, float scale,
+                                         int window, int num_splits, float* part_o, float* part_lse,
+                                         int chunk, int keep, const float* slopes, const float* sink, float softcap,
+                                         int maps, cudaStream_t stream) {
     if (n <= 0) return 0;
+    if (maps < 1 || d % (2 * maps) != 0 || softcap < 0.f || (softcap > 0.f && slopes)) return ACORN_ERR_UNSUPPORTED;
     if (!acorn_attention_decode_supported(nq, nkv, d) || num_splits < 1 || num_splits > DEC_MAX_SPLITS || n > 65535)
         return ACORN_ERR_UNSUPPORTED;
     if (num_splits > 1 && (part_o == nullptr || part_lse == nullptr)) return ACORN_ERR_UNSUPPORTED;
@@ -296,6 +333,7 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
     p.mask = AttnMask{window, chunk, keep}; p.num_splits = num_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes = slopes;
+    p.sink = sink; p.scale = scale; p.softcap = softcap; p.maps = maps;
     int rc;
     switch (d) {
         case 16: rc = launch_decode<16>(p, n, stream); break;

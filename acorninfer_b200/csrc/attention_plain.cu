@@ -13,7 +13,10 @@
 // output is [tokens, nq, dv]), which also serves a cache whose value rows are the key rows' heads
 // (v_pages == k_pages).  `sink` (one float per query head, or null) adds exp(sink) to the softmax
 // denominator.  `slopes` (one float per query head, or null) takes slope_h * (query position - key position)
-// off every score.
+// off every score.  `softcap` c > 0: the scaled score becomes c tanh(score / c) before all else.
+// `maps` n > 1: a query head holds n score maps side by side ([h][map][d / n] in a query row, nq counting
+// (head, map) pairs), and map a of a head is scored against entries a d/n .. (a + 1) d/n - 1 of the key row
+// only (a key row holds the maps' keys side by side): the pair's query is laid out with zeros elsewhere.
 //
 // A chunk is 512 keys.  Scores: one thread a key, the dot products of all the block's query heads
 // in one pass over the key row (the rows reach the threads through a hand-over in shared memory, so
@@ -35,7 +38,7 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     const T* __restrict__ v_pages, const int* __restrict__ block_table, const int* __restrict__ page_base,
     int table_stride, const int* __restrict__ token_row, const int* __restrict__ positions, int nq, int nkv, int d,
     int P, float scale, AttnMask mask, int parts, int dv, int v_row, const float* __restrict__ sink, int hpb,
-    const float* __restrict__ slopes) {
+    const float* __restrict__ slopes, float softcap, int maps) {
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                                   // [heads][d], scaled
     float* sc = smem + PLAIN_HEADS * d;                 // [heads][PLAIN_THREADS] probabilities of the chunk
@@ -55,8 +58,16 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
     const int lo = mask_lo(mask, pos), vlo = mask_vlo(mask, lo);     // virtual indices vlo..pos: kept keys, then lo..pos
     const int* table = block_table + (int64_t)r * table_stride - page_base[r];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int i = threadIdx.x; i < G * d; i += PLAIN_THREADS)
-        qs[i] = to_float(q[(int64_t)t * q_stride + (int64_t)(h0 + i / d) * d + i % d]) * scale;
+    if (maps > 1) {
+        const int dm = d / maps;                          // entries of one map
+        for (int i = threadIdx.x; i < G * d; i += PLAIN_THREADS) {
+            const int hv = h0 + i / d, e = i % d, a = hv % maps;
+            qs[i] = e / dm == a ? to_float(q[(int64_t)t * q_stride + (int64_t)hv * dm + (e - a * dm)]) * scale : 0.f;
+        }
+    } else {
+        for (int i = threadIdx.x; i < G * d; i += PLAIN_THREADS)
+            qs[i] = to_float(q[(int64_t)t * q_stride + (int64_t)(h0 + i / d) * d + i % d]) * scale;
+    }
 
     constexpr int NACC = PLAIN_MAX_D / PLAIN_LANES;
     const int dlane = threadIdx.x % PLAIN_LANES, kgroup = threadIdx.x / PLAIN_LANES;
@@ -142,7 +153,10 @@ __global__ void __launch_bounds__(PLAIN_THREADS) attention_plain_kernel(
                 const float dist = (float)(pos - mask_key(j, vlo, lo));
 #pragma unroll
                 for (int g = 0; g < PLAIN_HEADS; ++g)
-                    if (g < G) s[g] = slopes ? dot[g] - slopes[h0 + g] * dist : dot[g];
+                    if (g < G) {
+                        const float sv = softcap > 0.f ? softcap * tanhf(dot[g] / softcap) : dot[g];
+                        s[g] = slopes ? sv - slopes[h0 + g] * dist : sv;
+                    }
             }
         }
 #pragma unroll
@@ -243,8 +257,9 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
                                      int table_stride, const int* token_row, const int* positions,
                                      int tokens, int nq, int nkv, int d, int P, float scale, int window,
                                      int dtype, int dv, const float* sink, int chunk, int keep, int v_row,
-                                     const float* slopes, cudaStream_t stream) {
+                                     const float* slopes, float softcap, int maps, cudaStream_t stream) {
     if (tokens <= 0) return 0;
+    if (maps < 1 || d % maps != 0 || softcap < 0.f) return ACORN_ERR_UNSUPPORTED;
     if (dv < 1 || dv > PLAIN_MAX_D || v_row < dv) return ACORN_ERR_UNSUPPORTED;
     const AttnMask mask = {window, chunk, keep};
     if (d < 1 || d > PLAIN_MAX_D || nkv < 1 || nq % nkv != 0) return ACORN_ERR_UNSUPPORTED;
@@ -268,6 +283,6 @@ extern "C" int acorn_attention_plain(const void* q, int64_t q_stride, void* out,
     dim3 grid(tokens, nkv * parts);
     ACORN_DISPATCH_DTYPE(dtype, T, (attention_plain_kernel<T><<<grid, PLAIN_THREADS, smem, stream>>>(
         (const T*)q, q_stride, (T*)out, (const T*)k_pages, (const T*)v_pages, block_table, page_base,
-        table_stride, token_row, positions, nq, nkv, d, P, scale, mask, parts, dv, v_row, sink, hpb, slopes)));
+        table_stride, token_row, positions, nq, nkv, d, P, scale, mask, parts, dv, v_row, sink, hpb, slopes, softcap, maps)));
     return acorn_launch_status();
 }

@@ -9,6 +9,9 @@
 // S = Q K^T, causal mask by absolute positions (with a window, blocks of positions or kept first
 // keys: attention_mask.cuh; the keys are walked as virtual indices), online softmax in float32
 // (base 2), O += P V.  A tile may hold a single token (a decoded token in a mixed step).
+// Options: a cap c on the scaled scores (c tanh(score / c)); a sink per head (exp(sink) in the softmax
+// denominator, no key, no value); several score maps side by side in a head (`maps`: the query of the
+// (head, map) pair is laid out with zeros outside its map's entries of the key row, see attention_plain.cu).
 //
 // Reference: the reference gathers each request's K/V into a dense tensor per layer and
 // calls a library attention (acorninfer/models/qwen3.py:320-333, 367-381); the masks here are
@@ -34,6 +37,9 @@ struct PrefillParams {
     AttnMask mask;
     float scale_log2;
     const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
+    const float* sink;        // [nq] or null
+    float scale, softcap;     // the plain scale; softcap 0: none
+    int maps;                 // score maps side by side in a head (1: the usual head)
 };
 
 template <int D>
@@ -67,9 +73,17 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
         for (int i = 0; i < 4; ++i) {
             const int qi = (i & 1) ? qi1 : qi0;
             const int col = ks * 16 + 2 * tq + (i >> 1) * 8;
-            qa[ks][i] = qi < n_q ? *reinterpret_cast<const uint32_t*>(
-                                       p.q + (int64_t)(tok0 + qi) * p.q_stride + (int64_t)head * D + col)
-                                 : 0u;
+            if (p.maps > 1) {
+                const int dm = D / p.maps, a = head % p.maps;      // this (head, map) pair scores entries a dm .. of a key row
+                qa[ks][i] = (qi < n_q && col / dm == a)
+                                ? *reinterpret_cast<const uint32_t*>(p.q + (int64_t)(tok0 + qi) * p.q_stride +
+                                                                     (int64_t)head * dm + (col - a * dm))
+                                : 0u;
+            } else {
+                qa[ks][i] = qi < n_q ? *reinterpret_cast<const uint32_t*>(
+                                           p.q + (int64_t)(tok0 + qi) * p.q_stride + (int64_t)head * D + col)
+                                     : 0u;
+            }
         }
     float o[D / 8][4];
 #pragma unroll
@@ -126,7 +140,10 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
                     const int qp = qpos[e >> 1];
                     const int key = mask_key(v, vlo, lo);
                     const bool ok = v < hi && mask_sees(p.mask, qp, key);
-                    s[j][e] = ok ? fmaf(s[j][e], p.scale_log2, -slope_log2 * (float)(qp - key)) : -INFINITY;
+                    if (p.softcap > 0.f)
+                        s[j][e] = ok ? p.softcap * tanhf(s[j][e] * p.scale / p.softcap) * 1.4426950408889634f : -INFINITY;
+                    else
+                        s[j][e] = ok ? fmaf(s[j][e], p.scale_log2, -slope_log2 * (float)(qp - key)) : -INFINITY;
                     mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
                 }
             float corr[2], mref[2];
@@ -176,6 +193,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
     for (int h = 0; h < 2; ++h) {
         const int qi = h ? qi1 : qi0;
         if (qi >= n_q) continue;
+        if (p.sink) l_run[h] += exp2f(p.sink[head] * 1.4426950408889634f - m_run[h]);
         const float inv = 1.f / l_run[h];
         bf16* orow = p.out + ((int64_t)(tok0 + qi) * p.nq + head) * D;
 #pragma unroll
@@ -209,9 +227,12 @@ extern "C" int acorn_attention_prefill(const void* q, int64_t q_stride, void* ou
                                        const void* v_pages, const int* block_table, const int* page_base,
                                        int table_stride, const int* row_start, const int* row_pos,
                                        const int* tiles, int n_tiles, int nq, int nkv, int d, int P, float scale,
-                                       int window, int chunk, int keep, const float* slopes, cudaStream_t stream) {
+                                       int window, int chunk, int keep, const float* slopes, const float* sink,
+                                       float softcap, int maps, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!acorn_attention_prefill_supported(nq, nkv, d)) return ACORN_ERR_UNSUPPORTED;
+    // a map's entries are whole pairs of a fragment; a cap and a distance penalty do not go together
+    if (maps < 1 || d % (2 * maps) != 0 || softcap < 0.f || (softcap > 0.f && slopes)) return ACORN_ERR_UNSUPPORTED;
     PrefillParams p;
     p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out;
     p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
@@ -221,6 +242,7 @@ extern "C" int acorn_attention_prefill(const void* q, int64_t q_stride, void* ou
     p.mask = AttnMask{window, chunk, keep};
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes = slopes;
+    p.sink = sink; p.scale = scale; p.softcap = softcap; p.maps = maps;
     switch (d) {
         case 16: return launch_prefill<16>(p, n_tiles, stream);
         case 32: return launch_prefill<32>(p, n_tiles, stream);

@@ -142,7 +142,9 @@ extern "C" int acorn_add_rmsnorm(float* resid32, const void* delta, const float*
 // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) = z sigmoid(2 sqrt(2/pi) (z + 0.044715 z^3)).  A row of gu holds, per block of b
 // outputs, b gate values then b up values: gate of output i at (i / b) * 2b + i % b, up b further.
 // b = I is the plain layout [gate | up].
+// act 2, the capped form with `limit` L: g = min(gate, L), u = clamp(up, -L, L), out = g sigmoid(1.702 g) (u + 1).
 __device__ __forceinline__ float glu_act(float g, int act) {
+    if (act == 2) return g / (1.f + expf(-1.702f * g));          // the capped form's gate (the caps are the caller's)
     if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     return g / (1.f + expf(-g));
 }
@@ -154,7 +156,8 @@ template <int ACT> __device__ __forceinline__ float glu_act_fast(float g) {
 }
 
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int I, int b, int act) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int I, int b, int act,
+                              float limit) {
     pdl_wait();
     pdl_trigger();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -162,8 +165,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const int64_t t = idx / I;
         const int i = (int)(idx - t * I);
         const int64_t gi = t * 2 * I + (int64_t)(i / b) * 2 * b + i % b;
-        const float g = to_float(gu[gi]);
-        const float u = to_float(gu[gi + b]);
+        float g = to_float(gu[gi]);
+        float u = to_float(gu[gi + b]);
+        if (act == 2) {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit) + 1.f;
+        }
         out[idx] = from_float<T>(glu_act(g, act) * u);
     }
 }
@@ -207,12 +214,12 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
     }
 }
 
-extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int block, int dtype, int act,
+extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int block, int dtype, int act, float limit,
                             cudaStream_t stream) {
     const int64_t total = (int64_t)tokens * I;
     if (total <= 0) return 0;
-    if (block <= 0 || I % block != 0 || act < 0 || act > 1) return ACORN_ERR_UNSUPPORTED;
-    if (dtype == ACORN_DTYPE_BF16 && block % 8 == 0 && tokens <= 65535) {
+    if (block <= 0 || I % block != 0 || act < 0 || act > 2) return ACORN_ERR_UNSUPPORTED;
+    if (act < 2 && dtype == ACORN_DTYPE_BF16 && block % 8 == 0 && tokens <= 65535) {
         const int I8 = I / 8;
         int bx = (I8 + 511) / 512;                  // 256 threads, two chunks each
         if (bx < 1) bx = 1;
@@ -225,7 +232,7 @@ extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int bl
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
-                                                       (const T*)gu, (T*)out, total, I, block, act));
+                                                       (const T*)gu, (T*)out, total, I, block, act, limit));
     return ACORN_ERR_UNSUPPORTED;
 }
 
@@ -671,4 +678,87 @@ extern "C" int acorn_head_gate(const void* x, const void* g, int64_t ldg, void* 
                                                        (const T*)x, (const T*)g, ldg, (T*)out, ldo, heads, d, total,
                                                        scale));
     return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- two score maps of a head into one output
+// a [tokens, heads, 2, dv]: the outputs a1, a2 of a head's two attention maps over the same values.
+//   o = a1 - lambda a2;   o <- o / sqrt(mean(o^2) + eps) * scale;   out[t, h, :] = o * sigmoid(g[t * ldg + h dv + :])
+// (g: a slice of a wider product, a gate per output entry; null: no gate).  float32, one rounding.  A warp a
+// (token, head).
+template <typename T>
+__global__ void diff_combine_kernel(const T* __restrict__ a, const T* __restrict__ g, int64_t ldg, T* __restrict__ out,
+                                    int64_t items, int heads, int dv, float lambda, float scale, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int64_t t = item / heads;
+    const int h = (int)(item - t * heads);
+    const T* a1 = a + item * 2 * dv;
+    const T* a2 = a1 + dv;
+    float ss = 0.f;
+    for (int i = lane; i < dv; i += 32) {
+        const float o = to_float(a1[i]) - lambda * to_float(a2[i]);
+        ss += o * o;
+    }
+    ss = warp_sum(ss);
+    const float f = rsqrtf(ss / (float)dv + eps) * scale;
+    for (int i = lane; i < dv; i += 32) {
+        float o = (to_float(a1[i]) - lambda * to_float(a2[i])) * f;
+        if (g) o = o / (1.f + expf(-to_float(g[t * ldg + (int64_t)h * dv + i])));
+        out[item * dv + i] = from_float<T>(o);
+    }
+}
+
+extern "C" int acorn_diff_combine(const void* a, const void* g, int64_t ldg, void* out, int tokens, int heads, int dv,
+                                  float lambda, float scale, float eps, int dtype, cudaStream_t stream) {
+    const int64_t items = (int64_t)tokens * heads;
+    if (items <= 0) return 0;
+    if (dv < 1) return ACORN_ERR_UNSUPPORTED;
+    const int warps = 8;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(diff_combine_kernel<T>, dim3((unsigned)((items + warps - 1) / warps)),
+                                                       dim3(32 * warps), 0, stream, (const T*)a, (const T*)g, ldg, (T*)out,
+                                                       items, heads, dv, lambda, scale, eps));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- two float32 streams side by side, rounded
+// out[t] = [a[t] | b[t]] in the activation dtype: the input of a product over both streams.
+template <typename T>
+__global__ void pair_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int64_t total,
+                                 int H) {
+    pdl_wait();
+    pdl_trigger();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / (2 * H);
+        const int c = (int)(i - t * 2 * H);
+        out[i] = from_float<T>(c < H ? a[t * H + c] : b[t * H + c - H]);
+    }
+}
+
+extern "C" int acorn_pair_rows(const float* a, const float* b, void* out, int tokens, int H, int dtype, cudaStream_t stream) {
+    const int64_t total = (int64_t)tokens * 2 * H;
+    if (total <= 0) return 0;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(pair_rows_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, a, b,
+                                                       (T*)out, total, H));
+    return ACORN_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- x[t, :] += row (float32): one vector added to every row
+__global__ void add_row_kernel(float* __restrict__ x, const float* __restrict__ row, int64_t total, int H) {
+    pdl_wait();
+    pdl_trigger();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+        x[i] += row[i % H];
+}
+
+extern "C" int acorn_add_row(float* x, const float* row, int tokens, int H, cudaStream_t stream) {
+    const int64_t total = (int64_t)tokens * H;
+    if (total <= 0) return 0;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    return acorn_launch(add_row_kernel, dim3((int)blocks), dim3(256), 0, stream, x, row, total, H);
 }

@@ -46,7 +46,7 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
                                   int table_stride, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                   int tokens, int nq, int nkv, int d, int rot, int pairing, int P,
                                   float eps, int write_kv, int64_t ld, int dv, int v_from_k, QkConv cv,
-                                  T* __restrict__ q_out, int64_t ld_q) {
+                                  T* __restrict__ q_out, int64_t ld_q, float magnitude, int norm_after) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_trigger();
@@ -115,7 +115,7 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
         ss += v * v;
     }
     const float* w = (h < nq) ? q_w : k_w;
-    if (w) {
+    if (w && !norm_after) {
         ss = warp_sum(ss);
         const float inv = rsqrtf(ss / (float)d + eps);
         __syncwarp();
@@ -123,11 +123,37 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
     }
     __syncwarp();
     const int half = rot >> 1;
+    if (norm_after) {
+        // the rotation first (cos and sin times `magnitude`), then the head brought to unit root mean square
+        // (times the weight, if one is given): the rotated part's length depends on the magnitude
+        float ss2 = 0.f;
+        for (int j = lane; j < half; j += 32) {
+            const int ia = pairing == 0 ? j : 2 * j;
+            const int ib = pairing == 0 ? j + half : 2 * j + 1;
+            float s, c;
+            sincosf((float)pos * inv_freq[j], &s, &c);
+            s *= magnitude;
+            c *= magnitude;
+            const float a = x[ia], b = x[ib];
+            const float ra = a * c - b * s, rb = b * c + a * s;
+            x[ia] = ra;
+            x[ib] = rb;
+            ss2 += ra * ra + rb * rb;
+        }
+        for (int i = rot + lane; i < d; i += 32) ss2 += x[i] * x[i];
+        ss2 = warp_sum(ss2);
+        const float inv = rsqrtf(ss2 / (float)d + eps);
+        __syncwarp();
+        for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(x[i] * inv * (w ? w[i] : 1.f));
+        return;
+    }
     for (int j = lane; j < half; j += 32) {
         const int ia = pairing == 0 ? j : 2 * j;
         const int ib = pairing == 0 ? j + half : 2 * j + 1;
         float s, c;
         sincosf((float)pos * inv_freq[j], &s, &c);
+        s *= magnitude;
+        c *= magnitude;
         const float a = x[ia], b = x[ib];
         dst[ia] = from_float<T>(a * c - b * s);
         dst[ib] = from_float<T>(b * c + a * s);
@@ -387,7 +413,8 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
                                 float eps, int write_kv, int dtype, int64_t ld, int dv, int v_from_k,
                                 const float* conv_w, int taps, const float* bias, float* state,
                                 int64_t slot_stride, int64_t conv_off, const int* row_start, const int* row_slot,
-                                void* q_out, int64_t ld_q, int update_single, cudaStream_t stream) {
+                                void* q_out, int64_t ld_q, int update_single, float magnitude, int norm_after,
+                                cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d > 1024 || rot > d || (rot & 1) || dv < 1 || dv > 1024 || (v_from_k && dv != d)) return ACORN_ERR_UNSUPPORTED;
     QkConv cv;
@@ -397,8 +424,9 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
     if (conv_w && (taps < 1 || taps > QK_MAX_TAPS || v_from_k || q_out == nullptr || row_start == nullptr ||
                    (taps > 1 && (state == nullptr || row_slot == nullptr))))
         return ACORN_ERR_UNSUPPORTED;
+    const bool special = magnitude != 1.f || norm_after;            // the general kernel alone knows these
     const bool plain_rows = conv_w == nullptr && bias == nullptr && q_out == nullptr;
-    if (plain_rows && rot == d && pairing == 0 && dv == d && !v_from_k && ld == (int64_t)(nq + 2 * nkv) * d &&
+    if (plain_rows && !special && rot == d && pairing == 0 && dv == d && !v_from_k && ld == (int64_t)(nq + 2 * nkv) * d &&
         (d == 16 || d == 32 || d == 64 || d == 128 || d == 256)) {
 #define ROPE_VEC(G)                                                                                                  \
     ACORN_DISPATCH_DTYPE(dtype, T, return (launch_rope_vec<T, G>((T*)qkv, q_w, k_w, inv_freq, positions, token_row,   \
@@ -415,7 +443,7 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
 #undef ROPE_VEC
     }
     const int vec_taps = conv_w ? taps : 0;
-    if (!plain_rows && rot == 0 && !v_from_k && vec_taps <= 4 && d % 4 == 0 && dv % 4 == 0 && d <= 128 && dv <= 128 &&
+    if (!plain_rows && !special && rot == 0 && !v_from_k && vec_taps <= 4 && d % 4 == 0 && dv % 4 == 0 && d <= 128 && dv <= 128 &&
         ld % 4 == 0 && ld_q % 4 == 0 && slot_stride % 4 == 0 && conv_off % 4 == 0 && qk_aligned16(qkv) &&
         qk_aligned16(q_out) && qk_aligned16(k_pages) && qk_aligned16(v_pages) && qk_aligned16(q_w) &&
         qk_aligned16(k_w) && qk_aligned16(conv_w) && qk_aligned16(bias) && qk_aligned16(state)) {
@@ -441,7 +469,7 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(
         qk_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, (T*)qkv, q_w, k_w, inv_freq,
         positions, token_row, block_table, page_base, table_stride, (T*)k_pages, (T*)v_pages, tokens, nq, nkv, d, rot,
-        pairing, P, eps, write_kv, ld, dv, v_from_k, cv, (T*)q_out, ld_q));
+        pairing, P, eps, write_kv, ld, dv, v_from_k, cv, (T*)q_out, ld_q, magnitude, norm_after));
     return ACORN_ERR_UNSUPPORTED;
 }
 

@@ -4,18 +4,19 @@
 //   moe_route     per token: s = softmax(z) over all N router outputs; the choice score is s + correction;
 //                 the outputs form `groups` equal groups of neighbours, a group's score is its largest choice
 //                 score, and only outputs of the `keep` best groups can be chosen; the `top` largest choice
-//                 scores win; their weights are s itself (not renormalized).  float32 throughout.
+//                 scores win; their weights are s itself, or with `normalize` s over the chosen's sum
+//                 (+ 1e-20).  float32 throughout.
 //   moe_plan      counts per expert, offsets (exclusive sums) and a slot for every (token, choice) pair,
 //                 so that the pairs of an expert are neighbours: slot_token[slot], slot_of[pair].
 //   grouped_gemm  C[slot, :] = A[row(slot), :] W_e^T for the slots of every expert e < E
-//   moe_combine   out[t] = sum_k weight_k * (chosen_k >= E ? x[t] : y[slot_of(t, k)])
+//   moe_combine   out[t] = sum_k weight_k * (chosen_k >= E ? x[t] : y[slot_of(t, k)]) (+ extra[t], if given)
 //                 (router outputs from E on are identity experts: they return their input)
 #include "mma_helpers.cuh"
 
 // One warp per token.  Ties go to the lower index.
 __global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction,
                                  int* __restrict__ idx, float* __restrict__ wts, int tokens, int N, int top, int groups,
-                                 int keep) {
+                                 int keep, int normalize) {
     extern __shared__ float sm[];                       // per warp: s[N], choice[N]
     pdl_wait();
     pdl_trigger();
@@ -98,10 +99,16 @@ __global__ void moe_route_kernel(const float* __restrict__ z, const float* __res
         }
         __syncwarp();
     }
+    if (normalize && lane == 0) {
+        float total = 0.f;
+        for (int k = 0; k < top; ++k) total += wts[(int64_t)t * top + k];
+        total += 1e-20f;
+        for (int k = 0; k < top; ++k) wts[(int64_t)t * top + k] /= total;
+    }
 }
 
 extern "C" int acorn_moe_route(const float* z, const float* correction, int* idx, float* wts, int tokens, int N, int top,
-                               int groups, int keep, cudaStream_t stream) {
+                               int groups, int keep, int normalize, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (N < 1 || top < 1 || top > N || groups < 1 || groups > 64 || N % groups || keep < 1 || keep > groups || N > 2048)
         return ACORN_ERR_UNSUPPORTED;
@@ -114,7 +121,7 @@ extern "C" int acorn_moe_route(const float* z, const float* correction, int* idx
         configured.mark();
     }
     return acorn_launch(moe_route_kernel, dim3((tokens + warps - 1) / warps), dim3(32 * warps), smem, stream, z, correction,
-                        idx, wts, tokens, N, top, groups, keep);
+                        idx, wts, tokens, N, top, groups, keep, normalize);
 }
 
 // One block: histogram of the chosen outputs, exclusive sums, then a slot for every pair.  Within an
@@ -451,7 +458,8 @@ extern "C" int acorn_grouped_gemm(const void* A, int64_t lda, const int* a_rows,
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict__ x, const int* __restrict__ slot_of,
                                    const int* __restrict__ idx, const float* __restrict__ wts, T* __restrict__ out, int H,
-                                   int top, int E, float* __restrict__ resid32, const float* __restrict__ norm_w, float eps) {
+                                   int top, int E, float* __restrict__ resid32, const float* __restrict__ norm_w, float eps,
+                                   const T* __restrict__ extra) {
     extern __shared__ float row_s[];                    // [H] the row's sums (fused form only)
     __shared__ float scratch[32];
     pdl_wait();
@@ -465,6 +473,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict_
             const float v = idx[p] >= E ? to_float(x[t * H + i]) : to_float(y[(int64_t)slot_of[p] * H + i]);
             acc = fmaf(wts[p], v, acc);
         }
+        if (extra) acc += to_float(extra[t * H + i]);      // what every token takes beside its choices (a shared expert)
         if (resid32) {
             row_s[i] = acc;
             ss += acc * acc;
@@ -484,11 +493,12 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict_
 
 extern "C" int acorn_moe_combine(const void* y, const void* x, const int* slot_of, const int* idx, const float* wts, void* out,
                                  int tokens, int H, int top, int E, int dtype, float* resid32, const float* norm_w, float eps,
-                                 cudaStream_t stream) {
+                                 const void* extra, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     const size_t smem = resid32 ? (size_t)H * sizeof(float) : 0;
     if (smem > 48 * 1024) return ACORN_ERR_UNSUPPORTED;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(moe_combine_kernel<T>, dim3(tokens), dim3(256), smem, stream, (const T*)y,
-                                                       (const T*)x, slot_of, idx, wts, (T*)out, H, top, E, resid32, norm_w, eps));
+                                                       (const T*)x, slot_of, idx, wts, (T*)out, H, top, E, resid32, norm_w, eps,
+                                                       (const T*)extra));
     return ACORN_ERR_UNSUPPORTED;
 }

@@ -122,17 +122,25 @@ def _key_bound(table_keys: int, window: int | None, chunk: int | None, keep_firs
 def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, d: int, scale: float,
                     window: int | None, chunk: int | None = None, keep_first: int = 0,
                     value_dim: int | None = None, slopes32: torch.Tensor | None = None,
-                    q: torch.Tensor | None = None) -> torch.Tensor:
+                    q: torch.Tensor | None = None, sink32: torch.Tensor | None = None, softcap: float | None = None,
+                    maps: int = 1) -> torch.Tensor:
     """Attention of all tokens of the step; q is the head of ``qkv`` ([T, >= nq d]).  ``window``, ``chunk``,
     ``keep_first``: which earlier keys a query reads (see ``parts/attention.py``); ``value_dim``: width of the
     value rows where it is not ``d``; ``slopes32`` (float32 [nq]): a penalty ``slope_h * distance to the key`` on
     the scores; ``q``: the queries where they are not the head of ``qkv`` ([T, >= nq d]).  The tensor-core kernels
-    take values as wide as keys; the TMA decode kernel knows windows only."""
+    take values as wide as keys; the TMA decode kernel knows windows only.  ``sink32`` (float32 [nq]): a term
+    ``exp(sink_h)`` in the softmax denominator; ``softcap`` c: the scaled score becomes ``c tanh(score / c)``; ``maps``
+    n > 1: every head holds n score maps side by side and ``nq`` counts (head, map) pairs (see
+    ``ops.attention_plain``).  The tcgen05 prefill kernel and the TMA decode kernel know none of the three: such
+    layers run the mma.sync prefill kernel and the cp.async split-K decode kernel."""
     if q is not None:
         qkv = q
     P = cache.k_pages.shape[2]
-    windowed_only = not chunk and not keep_first and slopes32 is None
+    scored = sink32 is not None or bool(softcap) or maps != 1           # what only some of the kernels know
+    windowed_only = not chunk and not keep_first and slopes32 is None and not scored
     mask = {"chunk": chunk, "keep_first": keep_first, "slopes32": slopes32}
+    if scored:
+        mask.update(sink32=sink32, softcap=softcap, maps=maps)
     if qkv.dtype == torch.bfloat16 and (value_dim is None or value_dim == d):
         if inputs.plan.all_decode and ops.attention_decode_supported(nq, nkv, d) and inputs.num_tokens <= 65535:
             bound = _key_bound(group.block_table.shape[1] * P, window, chunk, keep_first)
@@ -148,7 +156,7 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             # a mixed step: prompt portions through the prefill kernel, decoded tokens through the
             # decode kernel, both writing their rows of one output
             out = torch.empty((inputs.num_tokens, nq * d), dtype=qkv.dtype, device=qkv.device)
-            if ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0:
+            if ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0 and not scored:
                 # long rows on the tcgen05 kernel (tiles of 128 queries), short ones on the mma.sync kernel
                 if hx["attention.q_tiles_large"].shape[0]:
                     ops.attention_prefill_tc(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,

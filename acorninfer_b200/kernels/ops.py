@@ -91,7 +91,7 @@ class _Sigs:
     acorn_embed = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     acorn_patch_tokens = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     acorn_add_rmsnorm = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
-    acorn_swiglu = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_swiglu = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     acorn_add_layernorm = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                            c_int, c_void_p]
     acorn_add_into = [c_void_p, c_void_p, c_int64, c_int, c_void_p]
@@ -109,10 +109,10 @@ class _Sigs:
     acorn_qk_rope_kv = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                         c_int, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
-                        c_void_p, c_void_p, c_int64, c_int, c_void_p]
+                        c_void_p, c_void_p, c_int64, c_int, c_float, c_int, c_void_p]
     acorn_attention_plain = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                             c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+                             c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_int, c_void_p]
     acorn_bigram_add = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                         c_int, c_int, c_int, c_int, c_void_p]
     acorn_rmsnorm_add = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
@@ -142,7 +142,7 @@ class _Sigs:
                         c_void_p]
     acorn_delta_fold = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_delta_out = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
-    acorn_moe_route = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_moe_route = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_moe_plan = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_grouped_gemm = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_void_p]
@@ -151,10 +151,17 @@ class _Sigs:
                                   c_void_p]
     acorn_gather_rows = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                         c_void_p, c_void_p, c_float, c_void_p]
+                         c_void_p, c_void_p, c_float, c_void_p, c_void_p]
+    acorn_diff_combine = [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
+                          c_void_p]
+    acorn_pair_rows = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_add_row = [c_void_p, c_void_p, c_int, c_int, c_void_p]
     acorn_attention_decode = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                               c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    acorn_attention_decode_ex = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                 c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p]
     acorn_attention_decode_supported = [c_int, c_int, c_int]
     acorn_attention_decode_tma_main = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                        c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -165,7 +172,7 @@ class _Sigs:
     acorn_attention_decode_merge = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     acorn_attention_prefill = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                               c_int, c_int, c_void_p, c_void_p]
+                               c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p]
     acorn_attention_prefill_supported = [c_int, c_int, c_int]
     acorn_gemm_tc = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                      c_void_p]
@@ -381,12 +388,14 @@ def add_rmsnorm(resid32: torch.Tensor, delta: torch.Tensor | None, weight32: tor
     return out
 
 
-GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "capped_swish": 2}
+GLU_EPILOGUE_ACTIVATIONS = ("silu", "gelu_tanh")       # those the tcgen05 products apply themselves
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int | None = None,
-           activation: str = "silu") -> torch.Tensor:
-    """act(gate) * up, act silu or the tanh form of gelu.  A row holds, per block of ``block`` outputs, the gate values then the up
+           activation: str = "silu", limit: float = 0.0) -> torch.Tensor:
+    """act(gate) * up, act silu or the tanh form of gelu; or the capped form (``capped_swish`` with ``limit`` L):
+    ``g = min(gate, L), u = clamp(up, -L, L), g sigmoid(1.702 g) (u + 1)``.  A row holds, per block of ``block`` outputs, the gate values then the up
     values; the default (block = I) is the plain layout ``[gate | up]``."""
     _check(gate_up, "gate_up", None, 2)
     T, two_i = gate_up.shape
@@ -399,7 +408,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int | 
         out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     _check(out, "out", gate_up.dtype, 2)
     _ok(lib().acorn_swiglu(gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, block, dtype_code(gate_up.dtype),
-                           GLU_ACTIVATIONS[activation], _stream()), "swiglu")
+                           GLU_ACTIVATIONS[activation], float(limit), _stream()), "swiglu")
     return out
 
 
@@ -422,14 +431,17 @@ def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: t
                v_pages: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
                rotary_dim: int, interleaved: bool, eps: float, write_kv: bool = True,
                value_dim: int | None = None, values_from_keys: bool = False, bias32: torch.Tensor | None = None,
-               conv: "ShortConv | None" = None, q_out: torch.Tensor | None = None) -> None:
+               conv: "ShortConv | None" = None, q_out: torch.Tensor | None = None, magnitude: float = 1.0,
+               norm_after: bool = False) -> None:
     """Per-head q/k norm, rotary encoding, K/V page write; q is updated in place inside ``qkv``, or written
     to ``q_out`` [T, >= nq d] if that is given.  ``bias32`` (float32, one entry per channel of a row) is added to
     the row first; ``conv`` then runs a short causal convolution over time on every channel (``q_out`` is needed
     with it: a token's convolution reads its neighbours' rows as projected).
     ``value_dim``: width of a value head where it is not ``head_dim`` (the value pages then hold rows of
     that width).  ``values_from_keys``: the values are the keys as projected, before norm and rotation; a
-    row of ``qkv`` is then ``[q | k]``.  A row may be wider than its heads (further columns are ignored)."""
+    row of ``qkv`` is then ``[q | k]``.  A row may be wider than its heads (further columns are ignored).
+    ``magnitude``: a factor on cos and sin.  ``norm_after``: q and k heads are brought to unit root mean square
+    (``eps`` inside the root) after the rotation instead of before it, times their weight if one is given."""
     _check(qkv, "qkv", None, 2)
     T = qkv.shape[0]
     dv = head_dim if value_dim is None else int(value_dim)
@@ -488,7 +500,8 @@ def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: t
                                _ptr(conv.row_start) if conv is not None else None,
                                _ptr(conv.row_slot) if conv is not None else None,
                                _ptr(q_out), q_out.stride(0) if q_out is not None else 0,
-                               1 if (conv is not None and conv.update_single) else 0, _stream()),
+                               1 if (conv is not None and conv.update_single) else 0, float(magnitude),
+                               1 if norm_after else 0, _stream()),
         "qk_rope_kv")
 
 
@@ -510,15 +523,22 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
                     positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: int | None, out: torch.Tensor | None = None,
                     value_dim: int | None = None, sink32: torch.Tensor | None = None, chunk: int | None = None,
-                    keep_first: int = 0, slopes32: torch.Tensor | None = None) -> torch.Tensor:
+                    keep_first: int = 0, slopes32: torch.Tensor | None = None, softcap: float | None = None,
+                    maps: int = 1) -> torch.Tensor:
     """Paged causal attention for any mix of rows; ``q`` may be the head of a wider buffer
     (row stride ``q_stride`` elements).  Returns [tokens, nq * value_dim].  ``value_dim`` (default
     ``head_dim``): the leading entries of a value row that are summed; ``v_pages`` may be ``k_pages``
     itself.  ``sink32`` (float32 [nq]): a learned term exp(sink) per query head in the softmax denominator.
     ``window`` / ``chunk`` / ``keep_first``: which earlier keys a query reads (the last ``window``
     positions; those of its own block of ``chunk`` positions; and always the request's first ``keep_first``).
-    ``slopes32`` (float32 [nq]): ``slope_h * (query position - key position)`` is taken off every score."""
+    ``slopes32`` (float32 [nq]): ``slope_h * (query position - key position)`` is taken off every score.
+    ``softcap`` c: the scaled score becomes ``c tanh(score / c)``.  ``maps`` n > 1: every head holds n score maps
+    side by side (a query row is [head][map][head_dim / n], ``num_heads`` counts (head, map) pairs, a key row holds
+    the maps' keys side by side, and pair (h, a) is scored against entries a of the key row only); the output
+    is [tokens, num_heads (pairs), value_dim]."""
     _check_slopes(slopes32, num_heads)
+    if maps < 1 or head_dim % maps:
+        raise KernelError(f"attention: {maps} score maps do not divide a key row of {head_dim}")
     dv = head_dim if value_dim is None else int(value_dim)
     if not (1 <= dv <= v_pages.shape[3]):
         raise KernelError(f"value_dim must be in 1..{v_pages.shape[3]} (the value rows' width), got {dv}")
@@ -541,9 +561,17 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
                                     block_table.stride(0), token_row.data_ptr(), positions.data_ptr(),
                                     num_tokens, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
                                     float(scale), int(window or 0), dtype_code(q.dtype), dv, _ptr(sink32),
-                                    int(chunk or 0), int(keep_first or 0), v_pages.shape[3], _ptr(slopes32), _stream()),
+                                    int(chunk or 0), int(keep_first or 0), v_pages.shape[3], _ptr(slopes32),
+                                    float(softcap or 0.0), int(maps), _stream()),
         "attention_plain")
     return out
+
+
+def _check_sink(sink32: torch.Tensor | None, num_heads: int) -> None:
+    if sink32 is not None:
+        _check(sink32, "sink", torch.float32, 1)
+        if sink32.numel() != num_heads:
+            raise KernelError("sink must have one entry per query head")
 
 
 def _check_slopes(slopes32: torch.Tensor | None, num_heads: int) -> None:
@@ -567,14 +595,17 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
                      scale: float, window: int | None, num_splits: int, token_list: torch.Tensor | None = None,
                      out: torch.Tensor | None = None, scratch: tuple | None = None,
                      use_tma: bool | None = None, chunk: int | None = None, keep_first: int = 0,
-                     slopes32: torch.Tensor | None = None) -> torch.Tensor:
+                     slopes32: torch.Tensor | None = None, sink32: torch.Tensor | None = None,
+                     softcap: float | None = None, maps: int = 1) -> torch.Tensor:
     """Split-K decode attention (bfloat16) for single-token rows: the tokens 0..num_tokens-1, or
     those listed in ``token_list``.  ``out`` is [all tokens of the step, nq * d]; rows of tokens
     not handled are left as they are.  ``scratch`` = (part_o float32 [n, nq, splits, d],
     part_lse float32 [n, nq, splits]) is made here when absent and the kernel needs it (the TMA
-    kernel merges up to sixteen splits without; give ``scratch`` to force the separate merge pass)."""
+    kernel merges up to sixteen splits without; give ``scratch`` to force the separate merge pass).
+    ``sink32``, ``softcap``, ``maps``: as for ``attention_plain`` (the cp.async kernel only)."""
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode takes bfloat16")
+    _check_sink(sink32, num_heads)
     if not attention_decode_supported(num_heads, num_kv_heads, head_dim):
         raise KernelError(f"attention_decode does not take nq={num_heads}, nkv={num_kv_heads}, d={head_dim}")
     _check(k_pages, "k_pages", q.dtype, 4)
@@ -587,7 +618,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
         out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
     P = k_pages.shape[2]
     _check_slopes(slopes32, num_heads)
-    if chunk or keep_first or slopes32 is not None:
+    if chunk or keep_first or slopes32 is not None or sink32 is not None or softcap or maps != 1:
         if use_tma:
             raise KernelError("attention_decode: the TMA kernel knows windows only")
         use_tma = False
@@ -617,12 +648,13 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
                                                    _ptr(token_list), n, num_heads, head_dim, num_splits, _stream()),
                 "attention_decode_merge")
         return out
-    _ok(lib().acorn_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
-                                     block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
-                                     token_row.data_ptr(), positions.data_ptr(), _ptr(token_list), n, num_heads,
-                                     num_kv_heads, head_dim, P, float(scale), int(window or 0),
-                                     num_splits, _ptr(part_o), _ptr(part_lse), int(chunk or 0), int(keep_first or 0),
-                                     _ptr(slopes32), _stream()), "attention_decode")
+    _ok(lib().acorn_attention_decode_ex(q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+                                        block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
+                                        token_row.data_ptr(), positions.data_ptr(), _ptr(token_list), n, num_heads,
+                                        num_kv_heads, head_dim, P, float(scale), int(window or 0),
+                                        num_splits, _ptr(part_o), _ptr(part_lse), int(chunk or 0), int(keep_first or 0),
+                                        _ptr(slopes32), _ptr(sink32), float(softcap or 0.0), int(maps), _stream()),
+        "attention_decode")
     return out
 
 
@@ -635,10 +667,13 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_p
                       row_pos: torch.Tensor, tiles: torch.Tensor, num_tokens: int, num_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: int | None,
                       out: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0,
-                      slopes32: torch.Tensor | None = None) -> torch.Tensor:
+                      slopes32: torch.Tensor | None = None, sink32: torch.Tensor | None = None,
+                      softcap: float | None = None, maps: int = 1) -> torch.Tensor:
     """Tensor-core prefill attention (bfloat16) for the query tiles listed in ``tiles``
-    (int32 [n, 2]: row, first token within the row; 64 tokens a tile at most)."""
+    (int32 [n, 2]: row, first token within the row; 64 tokens a tile at most).  ``sink32``, ``softcap``,
+    ``maps``: as for ``attention_plain``."""
     _check_slopes(slopes32, num_heads)
+    _check_sink(sink32, num_heads)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill takes bfloat16")
     if not attention_prefill_supported(num_heads, num_kv_heads, head_dim):
@@ -653,7 +688,8 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_p
                                       block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
                                       row_start.data_ptr(), row_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0],
                                       num_heads, num_kv_heads, head_dim, k_pages.shape[2], float(scale),
-                                      int(window or 0), int(chunk or 0), int(keep_first or 0), _ptr(slopes32), _stream()),
+                                      int(window or 0), int(chunk or 0), int(keep_first or 0), _ptr(slopes32),
+                                      _ptr(sink32), float(softcap or 0.0), int(maps), _stream()),
         "attention_prefill")
     return out
 
@@ -1726,8 +1762,9 @@ def gated_norm(y32: torch.Tensor, gate: torch.Tensor, weight32: torch.Tensor, ep
 # ------------------------------------------------------------------ routed experts
 
 
-def moe_route(z32: torch.Tensor, correction32: torch.Tensor, top: int, groups: int, keep: int):
-    """(chosen [T, top] int32, weights [T, top] float32) from router logits z [T, N]."""
+def moe_route(z32: torch.Tensor, correction32: torch.Tensor, top: int, groups: int, keep: int, normalize: bool = False):
+    """(chosen [T, top] int32, weights [T, top] float32) from router logits z [T, N].  ``normalize``: the
+    chosen outputs' scores are divided by their sum (+ 1e-20)."""
     _check(z32, "router logits", torch.float32, 2)
     _check(correction32, "correction", torch.float32, 1)
     T, N = z32.shape
@@ -1736,7 +1773,7 @@ def moe_route(z32: torch.Tensor, correction32: torch.Tensor, top: int, groups: i
     idx = torch.empty((T, top), dtype=torch.int32, device=z32.device)
     wts = torch.empty((T, top), dtype=torch.float32, device=z32.device)
     _ok(lib().acorn_moe_route(z32.data_ptr(), correction32.data_ptr(), idx.data_ptr(), wts.data_ptr(), T, N, int(top),
-                              int(groups), int(keep), _stream()), "moe_route")
+                              int(groups), int(keep), 1 if normalize else 0, _stream()), "moe_route")
     return idx, wts
 
 
@@ -1797,11 +1834,16 @@ def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, 
 
 def moe_combine(y: torch.Tensor, x: torch.Tensor, slot_of: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor,
                 num_experts: int, resid32: torch.Tensor | None = None, weight32: torch.Tensor | None = None,
-                eps: float = 0.0) -> torch.Tensor | None:
+                eps: float = 0.0, extra: torch.Tensor | None = None) -> torch.Tensor | None:
     """out[t] = sum_k wts[t, k] * (idx[t, k] >= num_experts ? x[t] : y[slot_of[t, k]]).  With ``resid32`` the
     float32 sum is not returned but RMS-normed (``weight32``, ``eps``) and added to ``resid32`` in place; what
-    is returned is then the new stream rounded to ``x``'s dtype (None if that is float32)."""
+    is returned is then the new stream rounded to ``x``'s dtype (None if that is float32).  ``extra`` [T, H]: added
+    to every token's sum (what all tokens take beside their choices: a shared expert)."""
     _check(y, "y", x.dtype, 2)
+    if extra is not None:
+        _check(extra, "extra", x.dtype, 2)
+        if extra.shape != x.shape:
+            raise KernelError("moe_combine: extra does not fit")
     _check(x, "x", None, 2)
     T, H = x.shape
     fused = resid32 is not None
@@ -1813,8 +1855,50 @@ def moe_combine(y: torch.Tensor, x: torch.Tensor, slot_of: torch.Tensor, idx: to
     out = None if (fused and x.dtype == torch.float32) else torch.empty_like(x)
     _ok(lib().acorn_moe_combine(y.data_ptr(), x.data_ptr(), slot_of.data_ptr(), idx.data_ptr(), wts.data_ptr(), _ptr(out),
                                 T, H, idx.shape[1], int(num_experts), dtype_code(x.dtype), _ptr(resid32), _ptr(weight32),
-                                float(eps), _stream()), "moe_combine")
+                                float(eps), _ptr(extra), _stream()), "moe_combine")
     return out
+
+
+
+def diff_combine(a: torch.Tensor, gate: torch.Tensor | None, heads: int, value_dim: int, lam: float, scale: float,
+                 eps: float) -> torch.Tensor:
+    """a [T, heads * 2 * value_dim]: per head the outputs a1, a2 of its two score maps.  Returns
+    ``unit_rms(a1 - lam a2) * scale * sigmoid(gate)`` [T, heads * value_dim] (``gate`` [T, >= heads * value_dim], a
+    slice of a wider buffer, or None); float32 arithmetic, one rounding."""
+    _check(a, "a", None, 2)
+    T = a.shape[0]
+    if a.shape[1] != heads * 2 * value_dim:
+        raise KernelError(f"diff_combine: a {tuple(a.shape)} is not [T, {heads} * 2 * {value_dim}]")
+    if gate is not None and (gate.dtype != a.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[0] != T
+                             or gate.shape[1] < heads * value_dim):
+        raise KernelError(f"diff_combine: gate {tuple(gate.shape)} {gate.dtype} does not fit")
+    out = torch.empty((T, heads * value_dim), dtype=a.dtype, device=a.device)
+    _ok(lib().acorn_diff_combine(a.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), T,
+                                 heads, value_dim, float(lam), float(scale), float(eps), dtype_code(a.dtype), _stream()),
+        "diff_combine")
+    return out
+
+
+def pair_rows(a32: torch.Tensor, b32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``[a | b]`` of two float32 streams [T, H], rounded to ``dtype``: [T, 2 H]."""
+    _check(a32, "a", torch.float32, 2)
+    _check(b32, "b", torch.float32, 2)
+    if a32.shape != b32.shape:
+        raise KernelError("pair_rows: the streams differ in shape")
+    out = torch.empty((a32.shape[0], 2 * a32.shape[1]), dtype=dtype, device=a32.device)
+    _ok(lib().acorn_pair_rows(a32.data_ptr(), b32.data_ptr(), out.data_ptr(), a32.shape[0], a32.shape[1], dtype_code(dtype),
+                              _stream()), "pair_rows")
+    return out
+
+
+def add_row(x32: torch.Tensor, row32: torch.Tensor) -> torch.Tensor:
+    """x32 [T, H] += row32 [H], in place (float32)."""
+    _check(x32, "x", torch.float32, 2)
+    _check(row32, "row", torch.float32, 1)
+    if row32.numel() != x32.shape[1]:
+        raise KernelError("add_row: the row does not fit")
+    _ok(lib().acorn_add_row(x32.data_ptr(), row32.data_ptr(), x32.shape[0], x32.shape[1], _stream()), "add_row")
+    return x32
 
 # ------------------------------------------------------------------ sampling
 

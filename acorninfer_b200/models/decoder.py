@@ -17,8 +17,8 @@ import torch
 
 from .. import parts as _parts  # noqa: F401  (registers the built-in part kinds)
 from ..kernels import ops
-from ..parts.base import (BLOCKS, FEED_FORWARDS, LAYER_EXTRAS, MIXERS, NORMS, POSITION_ENCODINGS, STAGES, BuildContext, KVNeeds,
-                          ModelSpec, StateNeeds, TensorSpec, build_part)
+from ..parts.base import (BLOCKS, FEED_FORWARDS, LAYER_EXTRAS, MIXERS, NORMS, PASS_ENTRIES, POSITION_ENCODINGS, STAGES,
+                          BuildContext, KVNeeds, ModelSpec, StateNeeds, TensorSpec, build_part)
 
 
 @dataclass
@@ -66,7 +66,13 @@ class Decoder:
         for where in ("after_embedding", "before_head", "after_head"):
             self.stages[where] = [build_part(STAGES, ps, self.ctx) for ps in getattr(spec, where)]
             self._named_parts.extend((ps.prefix, st) for ps, st in zip(getattr(spec, where), self.stages[where]))
+        self.pass_entry = None
+        if spec.pass_entry is not None:
+            self.pass_entry = build_part(PASS_ENTRIES, spec.pass_entry, self.ctx)
+            self._named_parts.append((spec.pass_entry.prefix, self.pass_entry))
         for i, e in enumerate(spec.schedule):
+            if e.opens_pass is not None and self.pass_entry is None:
+                raise ValueError(f"schedule entry {i} opens a pass, but the model names no pass_entry part")
             if not (0 <= e.layer < len(spec.layers)):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}; the model has {len(spec.layers)}")
             if e.reads_cache_of is not None and not (0 <= e.reads_cache_of < i):
@@ -169,11 +175,15 @@ class Decoder:
         delta = None
         sched = self.spec.schedule
         # a run that takes the tokens in again adds the stream as it was here
-        entered32 = resid32.clone() if any(e.add_embedding for e in sched) else None
+        def reenters(e):
+            return e.add_embedding or e.opens_pass is not None
+
+        entered32 = resid32.clone() if any(reenters(e) for e in sched) else None
         for i, e in enumerate(sched):
-            if e.add_embedding:
+            if reenters(e):
+                # whatever the run before still has to add is added first: the stream is read whole here
                 if isinstance(delta, ops.NormedRows):
-                    raise ValueError(f"schedule entry {i} adds the token rows, but the run before it already "
+                    raise ValueError(f"schedule entry {i} takes the token rows in again, but the run before it already "
                                      "prepared this run's first norm")
                 if isinstance(delta, ops.DeltaPair):
                     delta = ops.fold_pair(resid32, delta)
@@ -183,11 +193,14 @@ class Decoder:
                 if delta is not None and not isinstance(delta, ops.RoundedRows):
                     ops.add_into(resid32, delta)
                 delta = None
-                ops.add_into(resid32, entered32)
+                if e.add_embedding:
+                    ops.add_into(resid32, entered32)
+                if e.opens_pass is not None:
+                    resid32 = self.pass_entry.forward(resid32, entered32, e.opens_pass, inputs)
             # the norm that consumes this run's output: the next run's first norm (the final norm
             # works on selected rows only and keeps its own kernel)
             nxt = self.blocks[sched[i + 1].layer].first_norm(inputs.num_tokens) \
-                if i + 1 < len(sched) and not sched[i + 1].add_embedding else None
+                if i + 1 < len(sched) and not reenters(sched[i + 1]) else None
             resid32, delta = self.blocks[e.layer].forward(resid32, delta, inputs, caches[i], next_norm=nxt)
             # two pending results (a block whose sublayers run side by side): whoever comes next adds both, or
             # the first is added here
@@ -195,7 +208,7 @@ class Decoder:
             if isinstance(delta, ops.DeltaPair) and not getattr(taker, "accepts_pair", False):
                 delta = ops.fold_pair(resid32, delta)
             # a normed sum left undone: the next block takes it into its first norm's kernel, or it is added here
-            if isinstance(delta, ops.NormedPending) and not (i + 1 < len(sched) and not sched[i + 1].add_embedding
+            if isinstance(delta, ops.NormedPending) and not (i + 1 < len(sched) and not reenters(sched[i + 1])
                                                              and getattr(taker, "accepts_normed_pending", False)):
                 delta.settle(resid32)
                 delta = None
@@ -207,6 +220,8 @@ class Decoder:
         for stage in self.stages["before_head"]:
             h = stage.forward(h, inputs)
         logits = ops.linear(h, self.head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0:
+            ops.head_gate(logits, None, 1, self.spec.logit_scale)       # every entry times the factor, in place
         for stage in self.stages["after_head"]:
             logits = stage.forward(logits, inputs)
         return logits

@@ -18,7 +18,10 @@ rule, the request's first ``keep_first`` keys.  Options: value heads of a width 
 projection and before the norm (``conv_taps``; the last ``conv_taps - 1`` projected rows of a request
 are its state, float32, in its state slot); a penalty on the distance to the key,
 ``score = q . k * scale - slope_h * (i - j)`` with ``slope_h = 2^(-slope_exponent * (h + 1) / heads)``
-(``slope_exponent``).
+(``slope_exponent``); the q/k norm applied after the rotation instead of before it (``norm_after_rotation``) and
+without weights (``qk_norm_weights`` false: the heads are only brought to unit root mean square); a learned sink per
+head, a term ``exp(sink_h)`` in the softmax denominator that has no key and no value (``sink``); a cap on the scaled
+scores, ``cap tanh(score / cap)`` (``softcap``).  A position encoding's factor on cos and sin (``magnitude``) is applied.
 
 All sizes are parameters.  The q, k, v (and gate) matrices are concatenated when bound so that one
 matrix product yields a token's whole row.  A run that reads another run's
@@ -36,7 +39,7 @@ from .base import MIXERS, BuildContext, CacheNeeds, KVNeeds, Mixer, StateNeeds, 
 _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
           "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "gate": "g_proj.weight",
           "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-          "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight"}
+          "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight", "sink": "sink"}
 
 
 @MIXERS.register("attention")
@@ -50,9 +53,16 @@ class Attention(Mixer):
                  window: int | None = None, chunk: int | None = None, keep_first: int = 0,
                  value_dim: int | None = None, values_from_keys: bool = False, head_gate: bool = False,
                  names: dict | None = None, bias: bool = False, conv_taps: int | None = None,
-                 slope_exponent: float | None = None):
+                 slope_exponent: float | None = None, norm_after_rotation: bool = False, qk_norm_weights: bool = True,
+                 sink: bool = False, softcap: float | None = None):
         """``names``: the tensors' names relative to the part's prefix (keys q, k, v, o, q_norm, k_norm, gate,
-        q_bias, k_bias, v_bias, q_conv, k_conv, v_conv)."""
+        q_bias, k_bias, v_bias, q_conv, k_conv, v_conv, sink)."""
+        if (norm_after_rotation or not qk_norm_weights) and (qk_norm_eps is None or conv_taps or bias):
+            raise ValueError("a q/k norm after the rotation or without weights needs qk_norm_eps and plain projections")
+        if not qk_norm_weights and not norm_after_rotation:
+            raise ValueError("a q/k norm without weights is built for the norm after the rotation only")
+        if softcap is not None and (not softcap > 0 or slope_exponent is not None):
+            raise ValueError("softcap must be > 0 and does not go with a distance penalty")
         if conv_taps is not None and (conv_taps < 1 or values_from_keys):
             raise ValueError("conv_taps must be >= 1 or None, and needs value columns of their own")
         if num_heads % num_kv_heads:
@@ -84,7 +94,11 @@ class Attention(Mixer):
                                          dtype=torch.float64).to(torch.float32)
         self.channels = (num_heads + num_kv_heads) * head_dim + (0 if values_from_keys else num_kv_heads * self.dv)
         self.bias32 = self.conv32 = None
-        self.plain = not (values_from_keys or head_gate or bias or conv_taps) and self.dv == head_dim
+        self.norm_after, self.norm_weights, self.sink, self.softcap = bool(norm_after_rotation), bool(qk_norm_weights), bool(sink), softcap
+        self.sink32 = None
+        magnitude = getattr(self.position, "magnitude", 1.0) if self.position is not None else 1.0
+        self.plain = (not (values_from_keys or head_gate or bias or conv_taps or self.norm_after or self.sink or softcap)
+                      and self.norm_weights and magnitude == 1.0 and self.dv == head_dim)
         self.gate_col = (self.nq + self.nkv) * self.d + (0 if values_from_keys else self.nkv * self.dv)
         self.w_qkv = self.w_o = self.q_norm32 = self.k_norm32 = None
 
@@ -99,9 +113,11 @@ class Attention(Mixer):
             specs[n["v"]] = TensorSpec((self.nkv * self.dv, self.hidden_size))
         if self.head_gate:
             specs[n["gate"]] = TensorSpec((self.nq, self.hidden_size))
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.norm_weights:
             specs[n["q_norm"]] = TensorSpec((self.d,), "norm")
             specs[n["k_norm"]] = TensorSpec((self.d,), "norm")
+        if self.sink:
+            specs[n["sink"]] = TensorSpec((self.nq,), "sink")
         rows = {"q": self.nq * self.d, "k": self.nkv * self.d, **({} if self.values_from_keys else {"v": self.nkv * self.dv})}
         for which, size in rows.items():
             if self.bias:
@@ -123,9 +139,11 @@ class Attention(Mixer):
         dtype = parts[0].dtype if all(p.dtype == parts[0].dtype for p in parts) else torch.float32
         self.w_qkv = torch.cat([p.to(dtype) for p in parts], dim=0).contiguous()
         self.w_o = tensors[n["o"]].contiguous()
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.norm_weights:
             self.q_norm32 = tensors[n["q_norm"]].to(torch.float32).contiguous()
             self.k_norm32 = tensors[n["k_norm"]].to(torch.float32).contiguous()
+        if self.sink:
+            self.sink32 = tensors[n["sink"]].to(torch.float32).contiguous()
         which = ("q", "k") + (() if self.values_from_keys else ("v",))
         if self.bias:
             self.bias32 = torch.cat([tensors[n[w + "_bias"]].to(torch.float32) for w in which]).contiguous()
@@ -185,7 +203,8 @@ class Attention(Mixer):
                            cache.k_pages, cache.v_pages, self.nq, self.nkv, self.d,
                            pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
                            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=True,
-                           value_dim=self.dv, bias32=self.bias32, conv=conv, q_out=qkv)
+                           value_dim=self.dv, bias32=self.bias32, conv=conv, q_out=qkv,
+                           magnitude=getattr(pos, "magnitude", 1.0) if pos is not None else 1.0)
             if self.taps and self.taps > 1 and inputs.plan.max_q_len > 1:     # rows of one token shifted their memory above
                 ops.conv_state_update(proj, cache.state, 0, inputs.row_start, inputs.row_slot, inputs.num_rows,
                                       self.channels, self.taps, bias32=self.bias32, skip_single=True)
@@ -197,10 +216,12 @@ class Attention(Mixer):
                            cache.k_pages, cache.v_pages, self.nq, self.nkv, self.d,
                            pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
                            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.write,
-                           value_dim=self.dv, values_from_keys=self.values_from_keys)
+                           value_dim=self.dv, values_from_keys=self.values_from_keys,
+                           magnitude=getattr(pos, "magnitude", 1.0) if pos is not None else 1.0,
+                           norm_after=self.norm_after)
         heads = attn_kernels.paged_attention(qkv, inputs, g, cache, self.nq, self.nkv, self.d, self.scale, self.window,
                                              chunk=self.chunk, keep_first=self.keep_first, value_dim=self.dv,
-                                             slopes32=self.slopes32)
+                                             slopes32=self.slopes32, sink32=self.sink32, softcap=self.softcap)
         if self.head_gate or out_scale != 1.0 or out is not None:
             gate_rows = qkv if proj is None else proj
             return ops.head_gate(heads, gate_rows[:, self.gate_col:] if self.head_gate else None, self.nq, out_scale, out=out)

@@ -16,6 +16,7 @@ Interfaces
 ``Block``             ``forward(resid32, delta, inputs, cache) -> (resid32, delta)``
 ``Stage``             ``forward(x, inputs) -> x`` outside the layers (after the token table, around the head)
 ``LayerExtra``        ``forward(resid32, rows, inputs)``: a further sublayer that adds to the stream itself
+``PassEntry``         ``forward(resid32, entered32, pass_index, inputs) -> resid32``: what opens a pass of a span of layers
 
 All activations are ``[tokens, width]`` over the flat token dimension of one step.
 The residual stream is kept in float32 (``resid32``); what a part adds to it
@@ -76,11 +77,14 @@ class ScheduleEntry:
     several entries.  ``reads_cache_of`` names an earlier entry whose cache this run
     reads instead of writing one of its own.  ``add_embedding``: the stream as it entered the first layer
     (the token rows after the stages that follow the token table) is added to the stream before this run:
-    a span of layers that runs several times in a row takes the tokens in again at each pass."""
+    a span of layers that runs several times in a row takes the tokens in again at each pass.  ``opens_pass`` n:
+    this run opens pass n (0, 1, ...) of such a span, and the model's ``pass_entry`` part transforms the stream
+    (from the stream itself, the stream as it entered the first layer, and n) before the run."""
 
     layer: int
     reads_cache_of: int | None = None
     add_embedding: bool = False
+    opens_pass: int | None = None
 
 
 @dataclass(frozen=True)
@@ -99,6 +103,8 @@ class ModelSpec:
     before_head: tuple[PartSpec, ...] = ()        # on the normed rows whose logits are wanted [wanted, hidden]
     after_head: tuple[PartSpec, ...] = ()         # on the float32 logits [wanted, vocab]
     embedding_scale: float = 1.0                  # factor on the token rows as they enter the stream (not on a tied head)
+    pass_entry: PartSpec | None = None            # kind of the PASS_ENTRIES registry: runs before entries with ``opens_pass``
+    logit_scale: float = 1.0                      # factor on the logits
 
 
 @dataclass
@@ -277,6 +283,15 @@ class LayerExtra(Part):
         raise NotImplementedError
 
 
+class PassEntry(Part):
+    """What opens a pass of a span of layers that runs several times: ``forward(resid32, entered32, pass_index,
+    inputs)`` returns the stream the pass's first layer reads (it may work in place); ``entered32`` is the stream
+    as it entered the model's first layer (the token rows), ``pass_index`` counts the passes from 0."""
+
+    def forward(self, resid32: torch.Tensor, entered32: torch.Tensor, pass_index: int, inputs: "Any") -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arrangement of a mixer, a feed-forward and norms around the residual stream."""
 
@@ -341,6 +356,7 @@ POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
 STAGES = Registry("model stage")
 LAYER_EXTRAS = Registry("layer extra")
+PASS_ENTRIES = Registry("pass entry")
 
 
 def build_part(registry: Registry, spec: PartSpec, ctx: BuildContext, **extra):

@@ -3,7 +3,8 @@
 ``prenorm``: ``x += mixer(norm_m(x)); x += feed_forward(norm_f(x))``
 (``Qwen3Block`` in ``acorninfer/models/qwen3.py:399-410``).  The residual stream is float32;
 each sum is fused into the norm that follows it, so a block takes ``(resid32, delta)``
-where ``delta`` is what the previous block still has to add, and returns the same pair.
+where ``delta`` is what the previous block still has to add, and returns the same pair.  A layer may have
+no feed-forward (the block is then its mixer's half alone).
 
 ``outnorm``: ``x += norm_m(mixer(x)); x += norm_f(feed_forward(x))``: the sublayers read the
 stream itself and only their outputs are normed (Kogonex).  The sums are done here, in float32, by
@@ -35,12 +36,12 @@ class PreNormBlock(Block):
 
     def __init__(self, ctx, mixer, feed_forward, norms):
         super().__init__(mixer, feed_forward, norms)
-        missing = {"mixer", "feed_forward"} - set(norms)
+        missing = ({"mixer", "feed_forward"} if feed_forward is not None else {"mixer"}) - set(norms)
         if missing:
             raise ValueError(f"prenorm block needs norms named 'mixer' and 'feed_forward'; missing {sorted(missing)}")
 
     def _fuses(self, num_rows):
-        return (self.mixer.supports_epilogue and self.feed_forward.supports_epilogue
+        return (self.feed_forward is not None and self.mixer.supports_epilogue and self.feed_forward.supports_epilogue
                 and self.mixer.fusable(num_rows) and self.feed_forward.fusable(num_rows))
 
     def first_norm(self, num_rows):
@@ -53,6 +54,10 @@ class PreNormBlock(Block):
         if isinstance(delta, ops.RoundedRows):          # the block before added its result itself
             delta = None
         h = delta if isinstance(delta, ops.NormedRows) else self.norms["mixer"].add_forward(resid32, delta)
+        if self.feed_forward is None:
+            if self.mixer.adds_residual:
+                return resid32, self.mixer.forward(h, inputs, cache, residual32=resid32)
+            return resid32, self.mixer.forward(h, inputs, cache)
         ep = self.norms["feed_forward"].as_epilogue(resid32) if fuse else None
         if ep is not None:
             h = self.mixer.forward(h, inputs, cache, epilogue=ep)

@@ -23,11 +23,13 @@ class SwiGLU(FeedForward):
     adds_residual = True
 
     def __init__(self, ctx: BuildContext, hidden_size: int, intermediate_size: int, activation: str = "silu",
-                 names: dict | None = None):
-        """``names``: the gate, up and down matrices' names relative to the part's prefix."""
+                 names: dict | None = None, limit: float = 0.0):
+        """``names``: the gate, up and down matrices' names relative to the part's prefix.  ``limit``: the cap of
+        the capped form (``capped_swish``: ``g = min(gate, L), u = clamp(up, -L, L), g sigmoid(1.702 g) (u + 1)``)."""
         if activation not in ops.GLU_ACTIVATIONS:
             raise ValueError(f"activation must be one of {sorted(ops.GLU_ACTIVATIONS)}, got {activation!r}")
-        self.activation = activation
+        self.activation, self.limit = activation, float(limit)
+        self.epilogue_act = activation in ops.GLU_EPILOGUE_ACTIVATIONS      # the tcgen05 products apply it themselves
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
         self.ctx = ctx
         self.hidden_size = hidden_size
@@ -55,7 +57,7 @@ class SwiGLU(FeedForward):
 
     def fusable(self, num_rows):
         widths = (2 * self.intermediate_size, self.hidden_size)                 # of the gate/up product and of the down product
-        return (ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
+        return (self.epilogue_act and ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
                 and self.w_gate_up.dtype == torch.bfloat16
                 and self.w_down.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
                 and self.intermediate_size % 8 == 0)
@@ -67,8 +69,8 @@ class SwiGLU(FeedForward):
         spared.  Measured: a gain from 384 rows on at hidden size 4,096 (a loss at 300 rows, where the
         second token tile is nearly empty); none at hidden size 1,024, where a tile's 16 k-steps are too
         few to hide its epilogue."""
-        return (self.ctx.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
-                and self.hidden_size >= ops.GEMM_PAIR_ALONE_MIN_K
+        return (self.epilogue_act and self.ctx.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16
+                and self.hidden_size % 8 == 0 and self.hidden_size >= ops.GEMM_PAIR_ALONE_MIN_K
                 and ops.pair_rows_ok(num_rows, 2 * self.intermediate_size, ops.device_sms(self.ctx.device),
                                      ops.GEMM_PAIR_MIN_FILL_ALONE, ops.GEMM_PAIR_ALONE_MAX_ROWS))
 
@@ -78,7 +80,7 @@ class SwiGLU(FeedForward):
             h = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, swiglu=True, activation=self.activation)
         else:
             gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype)
-            h = ops.swiglu(gu, block=self.block, activation=self.activation)
+            h = ops.swiglu(gu, block=self.block, activation=self.activation, limit=self.limit)
         return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype, epilogue=epilogue,
                           residual32=residual32 if epilogue is None else None)
 

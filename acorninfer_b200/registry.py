@@ -70,4 +70,4 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from .models import kogonex, qwen3, tedenex, vagulorn  # noqa: F401  (they register themselves)
+        from .models import kogonex, qwen3, tedenex, vagulorn, zigolix  # noqa: F401  (they register themselves)
