@@ -61,7 +61,7 @@ class DifferentialAttention(Mixer):
                  n["v"]: TensorSpec((self.G * self.dv, W)), n["gate"]: TensorSpec((self.H * self.dv, W)),
                  n["o"]: TensorSpec((W, self.H * self.dv))}
         for which in ("lq1", "lk1", "lq2", "lk2"):
-            specs[n[which]] = TensorSpec((self.d,), "bias")
+            specs[n[which]] = TensorSpec((self.d,), "lambda_part")
         if self.bias:
             specs[n["q_bias"]] = TensorSpec((self.H * 2 * self.d,), "bias")
             specs[n["k_bias"]] = TensorSpec((self.G * 2 * self.d,), "bias")

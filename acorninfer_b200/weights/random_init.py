@@ -169,6 +169,7 @@ INIT_KINDS.register("sink", lambda d: d.normal(1.0))                   # a softm
 INIT_KINDS.register("conv", lambda d: d.normal(0.5, 1.0 / d.shape[-1]))        # taps around an average
 INIT_KINDS.register("decay_log", lambda d: d.normal(0.5, -1.0))        # log of a decay rate: exp(.) around 0.4
 INIT_KINDS.register("norm_offset", lambda d: d.normal(d.sigma_norm))     # a norm weight stored as its distance from one
+INIT_KINDS.register("lambda_part", lambda d: d.normal(0.3))             # vectors whose products' sum is an exponent: kept small
 INIT_KINDS.register("blend", lambda d: d.normal(0.2, 0.5))             # shares of the row before in a blend of two rows
 
 

@@ -142,14 +142,19 @@ def capped_expert(h, w, prefix, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w(prefix + "down").T
 
 
-def routed_ff(h, f, w):
+def routed_ff(h, f, w, gaps=None):
     """The ``top`` experts of largest softmax score, weighted by their scores over the scores' sum, plus a
-    shared expert that every token takes."""
+    shared expert that every token takes.  ``gaps`` (a list) receives, per token, how far the last chosen
+    expert's router logit lies above the first one left out (infinity when all are chosen)."""
     E, top = f["router"]["experts"], f["router"]["top"]
-    s = torch.softmax(h @ w("router").T, dim=-1)
+    z = h @ w("router").T
+    s = torch.softmax(z, dim=-1)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        order = sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]
+        ranked = sorted(range(E), key=lambda e: (-float(s[t, e]), e))
+        order = ranked[:top]
+        if gaps is not None:
+            gaps.append(float(z[t, ranked[top - 1]] - z[t, ranked[top]]) if top < E else math.inf)
         total = sum(s[t, e] for e in order) + 1e-20
         for e in order:
             out[t] += (s[t, e] / total) * capped_expert(h[t:t + 1], w, f"e{e}.", f["expert"]["limit"])[0]
@@ -169,8 +174,9 @@ def layer_runs(cfg):
     return runs + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(cfg, tensors, tokens, return_layers=False):
-    """tokens: ids of one sequence.  float64 logits [T, vocab] (and the stream after every layer run)."""
+def forward(cfg, tensors, tokens, return_layers=False, router_gaps=None):
+    """tokens: ids of one sequence.  float64 logits [T, vocab] (and the stream after every layer run).
+    ``router_gaps`` (a list) receives one list per run of a routed feed-forward: see ``routed_ff``."""
     t64 = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps = cfg["norm"]["eps"]
     x0 = t64["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -186,7 +192,13 @@ def forward(cfg, tensors, tokens, return_layers=False):
         if f is not None:
             wf = lambda n, p=name: t64[f"{p}.mlp.{n}"]
             hh = norm(x, t64[name + ".norm2"], eps)
-            x = x + (dense_ff(hh, wf) if f.get("kind", "dense") == "dense" else routed_ff(hh, f, wf))
+            if f.get("kind", "dense") == "dense":
+                x = x + dense_ff(hh, wf)
+            else:
+                gaps = [] if router_gaps is not None else None
+                x = x + routed_ff(hh, f, wf, gaps)
+                if router_gaps is not None:
+                    router_gaps.append(gaps)
         after.append(x.clone())
     logits = (norm(x, t64["final.norm"], eps) @ t64["head"].T) * cfg.get("logit_scale", 1.0)
     return (logits, torch.stack(after)) if return_layers else logits

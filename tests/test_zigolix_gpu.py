@@ -1,0 +1,513 @@
+"""Zigolix on the GPU against the plain implementation (``tests/plain/zigolix.py``, float64).
+
+Whole models of several small configurations, replayed whole, with a decoded tail, in portions down to
+two tokens, and mixed with other requests in a pool so small that pages and slots are used again; every
+mechanism alone (a one-layer model, or its kernel with inputs made so that one key, a window's edge or
+the sink decides the result); long decoding; greedy generation through the public entry point and the
+scheduler.
+
+Errors are relative: the root mean square over the vocabulary of the difference of the logits (mean
+taken off) over the standard deviation of the plain model's logits.  Under bfloat16 a token whose router
+logits put the last chosen expert less than ``CLOSE`` above the first one left out may go to another expert
+than in float64 (the whole position then differs); such positions, which the plain implementation names, are
+left out of the bound on single positions, not of the mean.
+"""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from acorninfer_b200.config.model_config import LayerLoop, RotaryScaling, ZigolixConfig
+from tests import traces
+from tests.paged import rows_layout, scatter_to_pages
+from tests.plain import zigolix as plain
+from tests.tiny import random_tokens
+from tests.zigolix_tiny import ZIG_LONG, ZIGS, L, dif, make_model_dir, moe, random_config, read_weights, sink
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {"float32": 4e-5, "bfloat16": 0.1}
+CLOSE = 0.06
+LENGTHS = [45, 38, 61, 50, 33, 29]
+
+
+def rel_err(got, ref):
+    d = np.asarray(got, np.float64) - np.asarray(ref, np.float64)
+    d = d - d.mean()
+    return math.sqrt((d ** 2).mean()) / float(np.std(ref))
+
+
+@pytest.fixture(scope="module", params=list(ZIGS))
+def case(request, tmp_path_factory):
+    tiny = ZIGS[request.param]
+    d = make_model_dir(tmp_path_factory.mktemp(request.param), tiny)
+    w = read_weights(d)
+    reqs = {f"r{i}": random_tokens(n, tiny["cfg"].vocab_size, 4100 + i) for i, n in enumerate(LENGTHS)}
+    ref = plain_logits(tiny["cfg"], w, reqs)
+    return tiny, d, reqs, ref
+
+
+class Ref(dict):
+    """request -> float64 logits [T, vocab]; ``close``: the (request, position) pairs whose choice of experts
+    hangs on less than ``CLOSE``."""
+
+    close: set = frozenset()
+
+
+def plain_logits(cfg, w, reqs):
+    ref = Ref()
+    close = set()
+    for rid, toks in reqs.items():
+        gaps: list = []
+        ref[rid] = plain.forward(cfg.to_dict(), w, toks, router_gaps=gaps).numpy()
+        close |= {(rid, t) for run in gaps for t, g in enumerate(run) if g < CLOSE}
+    ref.close = close
+    return ref
+
+
+def run_cut(tiny, model_dir, steps, dtype, max_requests=4, watch=None):
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.replay import TraceSession
+
+    pool = traces.max_live_tokens(steps)
+    runner = ModelRunner.from_model_dir(model_dir, dtype=dtype, num_blocks=-(-pool // tiny["page_size"]),
+                                        page_size=tiny["page_size"], max_requests=max_requests, max_step_tokens=4096)
+    session = TraceSession(runner)
+
+    def step(msg):
+        if watch is None:
+            return session.step(msg)
+        out = session.step(dict(msg, end=[]))
+        watch(session, msg)
+        session.step({"entries": [], "end": msg["end"]})
+        return out
+
+    got = traces.collect(step, steps)
+    runner.manager.assert_balanced()
+    return got, runner
+
+
+def check(got, ref, dtype, what, tol=None):
+    """Every position within the tolerance; in bfloat16 a single position may come to twice the tolerance as long
+    as the mean over all positions stays below a third of it: a fault moves many positions, rounding few."""
+    errs = {key: rel_err(row, ref[key[0]][key[1]]) for key, row in got.items()}
+    tol = tol or TOL[dtype]
+    mean = float(np.mean(list(errs.values())))
+    close = getattr(ref, "close", set()) if dtype == "bfloat16" else set()
+    assert len(close & set(errs)) <= 0.5 * len(errs), f"{what}: too many close calls for the test to mean much"
+    worst = max((k for k in errs if k not in close), key=errs.get)
+    if dtype == "bfloat16":
+        assert errs[worst] < 2 * tol and mean < tol / 3, f"{what}: {worst}: {errs[worst]:.3e}, mean {mean:.3e}"
+    else:
+        assert errs[worst] < tol, f"{what}: {worst}: {errs[worst]:.3e}, mean {mean:.3e}"
+
+
+CUTS = {
+    "whole": traces.whole,
+    "decode_tail": lambda r: traces.decode_tail(r, tail=24),
+    "portions": lambda r: traces.portions(r, sizes=(7, 2, 5, 3, 16, 2, 11, 4)),
+    "mixed": lambda r: traces.mixed(r, max_live=4, seed=3, stagger=2),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", list(CUTS))
+def test_cut_matches_plain(case, cut, dtype):
+    tiny, d, reqs, ref = case
+    got, runner = run_cut(tiny, d, CUTS[cut](reqs), dtype)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    check(got, ref, dtype, cut)
+    if cut == "decode_tail":
+        assert runner.graph_replays >= len(reqs) * 10        # single-token steps replay captured graphs
+
+
+def test_cuts_agree_with_each_other_float32(case):
+    """The logits at a position do not depend on how the tokens were cut into steps, on what else was
+    in the batch or on which pages and slots held them, beyond rounding."""
+    tiny, d, reqs, _ = case
+    base, _ = run_cut(tiny, d, traces.whole(reqs), "float32")
+    for cut in ("decode_tail", "portions", "mixed"):
+        other, _ = run_cut(tiny, d, CUTS[cut](reqs), "float32")
+        for key, row in base.items():
+            assert rel_err(other[key], row) < 1e-5, f"{cut}: {key}"
+
+
+def test_mixed_trace_uses_pages_and_slots_again(case):
+    tiny, d, reqs, _ = case
+    steps = CUTS["mixed"](reqs)
+    pages: dict = {}
+    slots: dict = {}
+
+    def watch(session, msg):
+        for rid, rc in session.live.items():
+            slots.setdefault(rc.slot, set()).add(rid)
+            for table in rc.tables:
+                for page in table:
+                    pages.setdefault(page, set()).add(rid)
+
+    run_cut(tiny, d, steps, "float32", watch=watch)
+    assert len(slots) <= 4 and sum(1 for users in slots.values() if len(users) >= 2) >= 1, slots
+    assert sum(1 for users in pages.values() if len(users) >= 2) >= 2, pages
+
+
+def test_first_step_of_one_token_and_requests_left_out(case):
+    """A request whose first step is a single token (a window that holds one key, the sink against one score),
+    then portions beside another request that decodes and is left out of some steps."""
+    tiny, d, reqs, ref = case
+    a, b = reqs["r0"], reqs["r1"]
+    steps = [{"entries": [{"id": "r0", "tokens": a[:1], "want": [0]}], "end": []},
+             {"entries": [{"id": "r0", "tokens": a[1:3], "want": [0, 1]}, {"id": "r1", "tokens": b[:9], "want": list(range(9))}], "end": []},
+             {"entries": [{"id": "r1", "tokens": b[9:10], "want": [0]}], "end": []},
+             {"entries": [{"id": "r0", "tokens": a[3:20], "want": list(range(17))}, {"id": "r1", "tokens": b[10:11], "want": [0]}], "end": []},
+             {"entries": [{"id": "r0", "tokens": a[20:], "want": list(range(len(a) - 20))}], "end": ["r0"]},
+             {"entries": [{"id": "r1", "tokens": b[11:], "want": list(range(len(b) - 11))}], "end": ["r1"]}]
+    for i, s in enumerate(steps):
+        s["step"] = i
+    for dtype in ("float32", "bfloat16"):
+        got, _ = run_cut(tiny, d, steps, dtype)
+        check(got, ref, dtype, "first token alone")
+
+
+def test_long_decoding_float32(case):
+    """A short prompt and 170 decoded tokens: windows pass over decoded tokens many times and the pages behind
+    them are given back and taken again."""
+    tiny, d, _, _ = case
+    toks = random_tokens(190, tiny["cfg"].vocab_size, 79)
+    ref = plain_logits(tiny["cfg"], read_weights(d), {"long": toks})
+    got, _ = run_cut(tiny, d, traces.decode_tail({"long": toks}, tail=170), "float32")
+    check(got, ref, "float32", "long decoding")
+
+
+def test_long_requests_windows_over_pages(tmp_path):
+    """Requests of a few hundred tokens through windows of 70, 45 and 130 over pages of 16: the tensor-core kernels
+    walk several chunks of keys whose first and last are cut by the window, windowed groups give pages back while
+    a request is still fed."""
+    tiny = ZIG_LONG
+    reqs = {f"L{i}": random_tokens(n, tiny["cfg"].vocab_size, 710 + i) for i, n in enumerate([330, 260, 150])}
+    cuts = {"whole": traces.whole, "decode_tail": lambda r: traces.decode_tail(r, tail=90),
+            "portions": lambda r: traces.portions(r, sizes=(64, 3, 2, 128, 29, 16, 2, 70)),
+            "mixed": lambda r: traces.mixed(r, max_live=3, seed=5, max_portion=80, stagger=1)}
+    d = make_model_dir(tmp_path, tiny)
+    w = read_weights(d)
+    ref = plain_logits(tiny["cfg"], w, reqs)
+    for dtype in ("float32", "bfloat16"):
+        for cut, build in cuts.items():
+            got, runner = run_cut(tiny, d, build(reqs), dtype)
+            assert len(got) == sum(len(t) for t in reqs.values())
+            check(got, ref, dtype, f"long, {cut}")
+
+
+@pytest.mark.parametrize("seed", [2, 5, 8, 11])
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Models whose sizes are drawn from what real models have, requests of up to 300 tokens, whole, with a decoded
+    tail and mixed in a small pool, float32 and bfloat16."""
+    import random
+    tiny = dict(cfg=random_config(seed), page_size=16, seed=seed)
+    d = make_model_dir(tmp_path, tiny, sigma=0.06, sigma_norm=0.1)
+    w = read_weights(d)
+    rng = random.Random(seed)
+    lengths = [rng.randint(200, 300), rng.randint(100, 200), rng.randint(2, 60), 1, rng.randint(60, 150)]
+    reqs = {f"q{i}": random_tokens(n, tiny["cfg"].vocab_size, seed * 10 + i) for i, n in enumerate(lengths)}
+    ref = plain_logits(tiny["cfg"], w, reqs)
+    for dtype, tol in (("float32", 6e-5), ("bfloat16", 0.15)):
+        for cut, steps in (("whole", traces.whole(reqs)), ("decode_tail", traces.decode_tail(reqs, tail=40)),
+                           ("mixed", traces.mixed(reqs, max_live=4, seed=seed, max_portion=90, stagger=1))):
+            got, _ = run_cut(tiny, d, steps, dtype)
+            check(got, ref, dtype, f"seed {seed}, {cut}", tol=tol)
+
+
+def follows_plain(cfg, w, prompt, ids, slack, excuse_close=False):
+    gaps: list = []
+    logits = plain.forward(cfg.to_dict(), w, ids[:-1], router_gaps=gaps)
+    close = {t for run in gaps for t, g in enumerate(run) if g < CLOSE} if excuse_close else set()
+    return all(float(logits[i - 1].max() - logits[i - 1][ids[i]]) <= slack for i in range(len(prompt), len(ids))
+               if i - 1 not in close)
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-4), ("bfloat16", 0.3)])
+def test_greedy_generation_through_the_engine(case, dtype, slack):
+    """``generate``: the scheduler with a token budget (prompts cut into portions beside decoding
+    requests), sampling on the device, a step ahead of the host."""
+    from acorninfer_b200 import generate
+    tiny, d, _, _ = case
+    cfg = tiny["cfg"]
+    w = read_weights(d)
+    prompts = [random_tokens(n, cfg.vocab_size, 910 + n) for n in (1, 14, 23, 6, 31)]
+    outs = generate(d, prompts, max_new_tokens=12, temperature=0.0, dtype=dtype, page_size=tiny["page_size"],
+                    num_blocks=64, max_running=3, chunked_budget=10, watermark_blocks=0, eos_ids=())
+    for p, ids in zip(prompts, outs):
+        assert len(ids) == len(p) + 12 and follows_plain(cfg, w, p, ids, slack, dtype == "bfloat16"), (dtype, len(p))
+
+
+def test_preemption_recomputes_float32(case):
+    """So few pages that requests are preempted and recomputed from their first token."""
+    from acorninfer_b200.generation import build_engine, generate_with_engine
+    tiny, d, _, _ = case
+    cfg = tiny["cfg"]
+    prompts = [random_tokens(n, cfg.vocab_size, 50 + n) for n in (20, 18, 13)]
+    pages = -(-36 // tiny["page_size"]) * 2 + 1
+    tight = build_engine(d, dtype="float32", page_size=tiny["page_size"], num_blocks=pages, watermark_blocks=0, max_running=3)
+    got = generate_with_engine(tight, prompts, max_new_tokens=16, eos_ids=())
+    w = read_weights(d)
+    for p, a in zip(prompts, got):
+        assert len(a) == len(p) + 16 and follows_plain(cfg, w, p, a, 1e-4)
+
+
+# ------------------------------------------------------------------ one mechanism at a time
+
+
+def _solo(mixer, ff=None, width=48, vocab=90, loop=None, more=(), logit_scale=1.0):
+    return ZigolixConfig(vocab_size=vocab, hidden_size=width, norm_eps=1e-5, loop=loop, logit_scale=logit_scale,
+                         layers=(L(mixer, ff),) + tuple(more))
+
+
+_SMALL = sink(heads=1, kv_heads=1, dim=4, scale=0.5)
+SOLOS = {
+    "sink attention, nothing rotated, no window": _solo(sink(heads=3, kv_heads=3, dim=10, scale=0.6)),
+    "sink attention, whole head rotated, window of 1": _solo(sink(heads=2, kv_heads=1, dim=8, scale=0.5, mask=1, rot=8, base=100.0)),
+    "sink attention, two of 18 entries rotated, stretched": _solo(sink(heads=4, kv_heads=2, dim=18, scale=0.4, mask=7, rot=2, base=50.0,
+                                                                     scaling=RotaryScaling(8.0, 16, 2.0, 0.5))),
+    "sink attention, heads of 130, stretched, ramp inside": _solo(sink(heads=2, kv_heads=1, dim=130, scale=0.2, mask=13, rot=64, base=1e4,
+                                                                     scaling=RotaryScaling(3.0, 512, 20.0, 2.0))),
+    "sink attention, 9 query heads a key head": _solo(sink(heads=9, kv_heads=1, dim=16, scale=0.5, mask=12, rot=16)),
+    "differential, values wider than a key row": _solo(dif(heads=4, kv_heads=2, dim=3, vdim=22, scale=0.5, diff=0.3, softcap=2.0, mask=5)),
+    "differential, values narrower, no cap, no window": _solo(dif(heads=3, kv_heads=3, dim=9, vdim=4, scale=0.4, diff=0.8)),
+    "differential, one head, cap that bites": _solo(dif(heads=1, kv_heads=1, dim=8, vdim=16, scale=3.0, diff=0.5, softcap=0.5, mask=9)),
+    "differential, window of 1": _solo(dif(heads=2, kv_heads=1, dim=8, vdim=16, scale=0.4, diff=0.1, softcap=30.0, mask=1)),
+    "differential, 9 query heads a key head": _solo(dif(heads=9, kv_heads=1, dim=8, vdim=16, scale=0.4, diff=0.6, softcap=5.0, mask=20)),
+    "gated feed-forward, widths no multiple of 8": _solo(_SMALL, ff=37, width=44),
+    "experts: one choice of seven, no shared expert": _solo(_SMALL, ff=moe(11, 0.9, 7, 1)),
+    "experts: all three chosen, a wide shared expert with its own cap": _solo(_SMALL, ff=moe(8, 5.0, 3, 3, 40, 0.3)),
+    "experts: two of thirteen, caps that bite": _solo(_SMALL, ff=moe(24, 0.2, 13, 2, 8, 0.2), width=40),
+    "no feed-forward, a factor on the logits": _solo(sink(heads=2, kv_heads=2, dim=8, scale=0.5, mask=6, rot=4), logit_scale=0.3),
+    "one layer four times": _solo(dif(heads=2, kv_heads=1, dim=8, vdim=8, scale=0.3, diff=0.4, softcap=4.0, mask=9), ff=20, loop=LayerLoop(0, 1, 4)),
+    "a span that runs once": _solo(_SMALL, ff=16, loop=LayerLoop(0, 2, 1), more=(L(dif(2, 1, 4, 8, 0.5, 0.5), ff=None),)),
+    "the last two of three layers three times": _solo(_SMALL, ff=16, loop=LayerLoop(1, 3, 3), more=(
+        L(dif(heads=2, kv_heads=2, dim=6, vdim=6, scale=0.3, diff=0.6, mask=4), ff=moe(8, 1.0, 4, 2)),
+        L(sink(heads=2, kv_heads=1, dim=6, scale=0.4, mask=3, rot=6), ff=24))),
+}
+
+
+@pytest.mark.parametrize("name", list(SOLOS))
+def test_mechanism_alone(name, tmp_path):
+    tiny = dict(cfg=SOLOS[name], page_size=4, seed=7)
+    d = make_model_dir(tmp_path, tiny, sigma=0.3)
+    w = read_weights(d)
+    reqs = {f"s{i}": random_tokens(n, tiny["cfg"].vocab_size, 70 + i) for i, n in enumerate([26, 17, 9])}
+    ref = plain_logits(tiny["cfg"], w, reqs)
+    for cut in ("whole", "portions", "mixed", "decode_tail"):
+        steps = {"portions": traces.portions(reqs, sizes=(3, 2, 6, 2)), "decode_tail": traces.decode_tail(reqs, tail=8)}.get(cut) \
+            or CUTS[cut](reqs)
+        got, _ = run_cut(tiny, d, steps, "float32")
+        check(got, ref, "float32", f"{name}, {cut}")
+    got, _ = run_cut(tiny, d, CUTS["mixed"](reqs), "bfloat16")
+    check(got, ref, "bfloat16", f"{name}, mixed, bfloat16", tol=0.2)
+
+
+def ops():
+    from acorninfer_b200.kernels import ops as o
+    return o
+
+
+def _scored_attention(q, k, v, scale, window, sinks, cap, maps):
+    """Plain float64 attention of one row: q [S, nq, d / maps] ((head, map) pairs), k [S, nkv, d], v [S, nkv, dv]."""
+    S, nq, dm = q.shape
+    i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
+    ok = (j <= i) & ((i - j) < window if window else True)
+    out = []
+    for h in range(nq):
+        g, a = h // (nq // k.shape[1]), h % maps
+        s = q[:, h] @ k[:, g, a * dm:(a + 1) * dm].T * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        p = plain.sink_softmax(s[None], ok, None if sinks is None else sinks[h:h + 1])[0]
+        out.append(p @ v[:, g])
+    return torch.stack(out, 1)
+
+
+def _attention_case(befores, qlens, P, d, dv, nq, nkv, window, spikes, dtype, kernel, sinks=None, cap=None, maps=1, seed=0):
+    """Cache pages and queries for the attention kernels.  ``spikes``: (row, key position): that key and all
+    queries of the row get a large component along one direction of every map, so its score stands out wherever it
+    is seen.  ``nq`` counts (head, map) pairs; a key row has ``d`` entries, a pair's query ``d / maps``."""
+    o = ops()
+    g = torch.Generator().manual_seed(seed)
+    dm = d // maps
+    NP = sum(-(-(b + q) // P) for b, q in zip(befores, qlens)) + 5
+    lay = rows_layout(befores, qlens, P, NP, seed=seed)
+    k_pages = torch.zeros(NP, nkv, P, d, dtype=dtype, device=DEV)
+    v_pages = torch.zeros(NP, nkv, P, dv, dtype=dtype, device=DEV)
+    full = []
+    for r, (b, q) in enumerate(zip(befores, qlens)):
+        S = b + q
+        k = torch.randn(S, nkv, d, generator=g) * 0.3
+        v = torch.randn(S, nkv, dv, generator=g)
+        qq = torch.randn(S, nq, dm, generator=g) * 0.3
+        for (rr, j) in spikes:
+            if rr == r:
+                for a in range(maps):
+                    k[j, :, (a + 1) * dm - 1] = 6.0
+                qq[:, :, dm - 1] = 4.0
+        k, v, qq = k.to(dtype), v.to(dtype), qq.to(dtype)
+        scatter_to_pages(k_pages, lay["tables"][r], k, P)
+        scatter_to_pages(v_pages, lay["tables"][r], v, P)
+        full.append((qq.double(), k.double(), v.double()))
+    q_new = torch.cat([f[0][b:] for f, b in zip(full, befores)]).to(dtype).to(DEV).contiguous().view(-1, nq * dm)
+    scale = 0.5
+    s32 = None if sinks is None else sinks.float().to(DEV)
+    extra = dict(sink32=s32, softcap=cap, maps=maps)
+    common = (k_pages, v_pages, lay["block_table"], lay["page_base"])
+    if kernel == "plain":
+        out = o.attention_plain(q_new, nq * dm, *common, lay["token_row"], lay["positions"], lay["num_tokens"], nq, nkv,
+                                d, scale, window, value_dim=dv, **extra)
+    else:
+        i32 = dict(dtype=torch.int32, device=DEV)
+        starts = np.cumsum([0] + qlens)
+        out = torch.zeros((lay["num_tokens"], nq * dv), dtype=dtype, device=DEV)
+        tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if n > 1 for q0 in range(0, n, 64)], **i32).view(-1, 2)
+        if tiles.shape[0]:
+            o.attention_prefill(q_new, nq * dm, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
+                                lay["num_tokens"], nq, nkv, d, scale, window, out=out, **extra)
+        singles = torch.tensor([int(starts[r]) for r, n in enumerate(qlens) if n == 1], **i32)
+        if singles.numel():
+            o.attention_decode(q_new, nq * dm, *common, lay["token_row"], lay["positions"], lay["num_tokens"], nq, nkv, d,
+                               scale, window, int(kernel[-1]), token_list=singles, out=out, use_tma=False, **extra)
+    want = [_scored_attention(fq, fk, fv, scale, window, None if sinks is None else sinks.double(), cap, maps)[b:]
+            for (fq, fk, fv), b in zip(full, befores)]
+    return out.float().cpu().view(-1, nq, dv), torch.cat(want)
+
+
+# (dtype, tolerance, kernel, key row, value row, (head, map) pairs or heads, kv heads)
+KERNELS = [(torch.float32, 2e-5, "plain", 24, 10, 6, 3), (torch.bfloat16, 2e-2, "plain", 40, 56, 4, 1),
+           (torch.bfloat16, 2e-2, "mma1", 32, 32, 4, 2), (torch.bfloat16, 2e-2, "mma3", 96, 96, 6, 3),
+           (torch.bfloat16, 2e-2, "mma2", 128, 128, 8, 1)]
+
+
+@pytest.mark.parametrize("maps", [1, 2])
+@pytest.mark.parametrize("dtype,tol,kernel,d,dv,nq,nkv", KERNELS)
+def test_attention_window_sink_cap_and_maps(dtype, tol, kernel, d, dv, nq, nkv, maps):
+    """A sliding window, a sink per head, capped scores and two score maps a head in every attention kernel that
+    serves them: a spiked key decides the result while it is inside the window (the last position that still
+    sees it, at a page border, far back in a long row, in prompt rows and decoded tokens) and leaves it one
+    position later; the sink takes weight from every key; the cap flattens the spike."""
+    P, Wn = 16, 40
+    befores = [0, 100, 2 * Wn - 1, 2 * Wn, 139, 140, Wn, 0]
+    qlens = [200, 70, 1, 1, 1, 1, 2, 1]
+    # row 4 (position 139) is the last to see key 100 under a window of 40; row 5 (position 140) the first not to
+    spikes = [(0, 0), (0, 63), (0, 64), (0, 130), (1, 99), (1, 128), (2, Wn), (3, Wn), (4, 100), (5, 100), (6, 1), (6, 2)]
+    sinks = torch.linspace(-1.0, 3.0, nq, dtype=torch.float64)
+    got, want = _attention_case(befores, qlens, P, d, dv, nq, nkv, Wn, spikes, dtype, kernel, sinks, 30.0, maps)
+    assert (got - want).abs().max() < tol
+    at = np.cumsum([0] + qlens)
+    assert (got[at[4]] - got[at[5]]).abs().max() > 0.05           # one position on, the spiked key is gone
+    for sk, cp in ((None, 30.0), (sinks, None), (sinks, 1.5)):
+        other, want2 = _attention_case(befores, qlens, P, d, dv, nq, nkv, Wn, spikes, dtype, kernel, sk, cp, maps)
+        assert (other - want2).abs().max() < tol
+        assert (other - got).abs().max() > 0.02                  # neither the sink nor the cap is optional
+    for W2 in (1, 7, 64, 1000, None):
+        got, want = _attention_case([0, 99, 40], [70, 1, 3], P, d, dv, nq, nkv, W2, [(0, 20), (1, 98), (2, 41)],
+                                    dtype, kernel, sinks, 12.0, maps, seed=W2 or 3)
+        assert (got - want).abs().max() < tol, W2
+    # key 3 of 700 decides a decoded token and a prompt's rows when nothing hides it
+    got, want = _attention_case([0, 699], [40, 1], P, d, dv, nq, nkv, None, [(1, 3)], dtype, kernel, sinks, None, maps)
+    assert (got - want).abs().max() < tol
+
+
+def test_score_maps_combined_normed_and_gated():
+    """``unit_rms(a1 - lambda a2) (1 - diff) sigmoid(gate)`` per head, the gate a slice of a wider buffer."""
+    o = ops()
+    g = torch.Generator().manual_seed(1)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        for T, H, dv in ((5, 3, 7), (33, 2, 96), (1, 1, 130)):
+            a = torch.randn(T, H, 2, dv, generator=g).to(dtype)
+            wide = torch.randn(T, 11 + H * dv, generator=g).to(dtype)
+            lam, sc, eps = 0.83, 0.4, 1e-5
+            a64, g64 = a.double(), wide[:, 11:].double().view(T, H, dv)
+            want = plain.unit_rms(a64[:, :, 0] - lam * a64[:, :, 1], eps) * sc * torch.sigmoid(g64)
+            got = o.diff_combine(a.view(T, -1).to(DEV), wide.to(DEV)[:, 11:], H, dv, lam, sc, eps)
+            assert (got.float().cpu().view(T, H, dv) - want).abs().max() < tol
+            want = plain.unit_rms(a64[:, :, 0] - lam * a64[:, :, 1], eps) * sc
+            got = o.diff_combine(a.view(T, -1).to(DEV), None, H, dv, lam, sc, eps)
+            assert (got.float().cpu().view(T, H, dv) - want).abs().max() < tol
+
+
+def test_capped_gate_and_up():
+    """``min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)`` with values on both sides of the caps, in the
+    layout [gate | up] and with gate and up in turns."""
+    o = ops()
+    g = torch.Generator().manual_seed(2)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+        for T, I in ((4, 5), (19, 64)):
+            gate = (torch.randn(T, I, generator=g) * 3).to(dtype)
+            up = (torch.randn(T, I, generator=g) * 3).to(dtype)
+            for limit in (0.5, 2.0, 100.0):
+                gc, uc = gate.double().clamp(max=limit), up.double().clamp(-limit, limit)
+                want = gc * torch.sigmoid(1.702 * gc) * (uc + 1.0)
+                got = o.swiglu(torch.cat([gate, up], 1).to(DEV), activation="capped_swish", limit=limit)
+                assert (got.float().cpu() - want).abs().max() < tol * max(1.0, limit)
+                turns = torch.stack([gate, up], 2).reshape(T, 2 * I)
+                got = o.swiglu(turns.to(DEV), block=1, activation="capped_swish", limit=limit)
+                assert (got.float().cpu() - want).abs().max() < tol * max(1.0, limit)
+
+
+def test_router_weights_over_their_sum():
+    o = ops()
+    g = torch.Generator().manual_seed(3)
+    for T, N, top in ((9, 5, 2), (40, 12, 1), (3, 7, 7), (17, 64, 6)):
+        z = torch.randn(T, N, generator=g) * 2
+        idx, wts = o.moe_route(z.to(DEV), torch.zeros(N, device=DEV), top, 1, 1, normalize=True)
+        s = torch.softmax(z.double(), -1)
+        best = torch.topk(s, top, dim=-1)
+        assert torch.equal(idx.cpu().long(), best.indices)
+        assert (wts.cpu().double() - best.values / (best.values.sum(-1, keepdim=True) + 1e-20)).abs().max() < 1e-6
+
+
+def test_rotation_with_a_factor_then_unit_norm_and_keys_as_values():
+    """qk_rope_kv with a factor on cos and sin and the norm after the rotation, without weights: the queries in
+    place, the rotated and normed keys and the keys as projected (the values) in their pages."""
+    o = ops()
+    g = torch.Generator().manual_seed(4)
+    P = 4
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        for nq, nkv, d, rot in ((3, 1, 10, 4), (4, 2, 32, 32), (2, 2, 130, 64), (1, 1, 8, 0)):
+            befores, qlens = [5, 0, 9], [7, 3, 1]
+            lay = rows_layout(befores, qlens, P, 12, seed=d)
+            T = lay["num_tokens"]
+            rows = torch.randn(T, (nq + nkv) * d, generator=g).to(dtype)
+            rotp = {"dims": rot, "base": 77.0, "scaling": {"factor": 5.0, "original": 32, "fast": 4.0, "slow": 0.5}}
+            rate, mag = plain.stretched_frequencies(rotp) if rot else (torch.zeros(0, dtype=torch.float64), 1.0)
+            k_pages = torch.zeros(12, nkv, P, d, dtype=dtype, device=DEV)
+            v_pages = torch.zeros(12, nkv, P, d, dtype=dtype, device=DEV)
+            buf = rows.to(DEV).clone()
+            o.qk_rope_kv(buf, None, None, rate.float().to(DEV), lay["positions"], lay["token_row"], lay["block_table"],
+                         lay["page_base"], k_pages, v_pages, nq, nkv, d, rot, True, 1e-5, values_from_keys=True,
+                         magnitude=mag, norm_after=True)
+            pos = lay["positions"].cpu().double()
+            x = rows.double().view(T, nq + nkv, d)
+            y = x.clone()
+            if rot:
+                a = pos[:, None] * rate[None, :]
+                c, s = (torch.cos(a) * mag)[:, None, :], (torch.sin(a) * mag)[:, None, :]
+                u, v = x[..., 0:rot:2], x[..., 1:rot:2]
+                y[..., 0:rot:2], y[..., 1:rot:2] = u * c - v * s, v * c + u * s
+            y = plain.unit_rms(y, 1e-5)
+            assert (buf.float().cpu().view(T, nq + nkv, d)[:, :nq] - y[:, :nq]).abs().max() < tol
+            t = 0
+            for r, (b, n) in enumerate(zip(befores, qlens)):
+                for i in range(n):
+                    page, slot = lay["tables"][r][(b + i) // P], (b + i) % P
+                    assert (k_pages[page, :, slot].float().cpu() - y[t, nq:]).abs().max() < tol
+                    assert (v_pages[page, :, slot].float().cpu() - x[t, nq:]).abs().max() < tol      # as projected
+                    t += 1
+
+
+def test_pass_entry_kernels():
+    o = ops()
+    g = torch.Generator().manual_seed(5)
+    a, b = torch.randn(7, 12, generator=g), torch.randn(7, 12, generator=g)
+    for dtype in (torch.float32, torch.bfloat16):
+        got = o.pair_rows(a.to(DEV), b.to(DEV), dtype)
+        assert torch.equal(got.cpu(), torch.cat([a, b], 1).to(dtype))
+    row = torch.randn(12, generator=g)
+    assert torch.equal(o.add_row(a.to(DEV).clone(), row.to(DEV)).cpu(), a + row)
