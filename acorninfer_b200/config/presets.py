@@ -109,6 +109,33 @@ PRESETS.update({
 })
 
 
+def _zigolix(width: int, vocab: int, heads: int, kv_heads: int, ff: int, window: int, experts: int, top: int,
+             times: int = 2) -> dict:
+    """Layers in the pattern differential attention, differential attention with routed experts, attention with a sink,
+    twice, layers 1 and 2 run ``times`` times in a row; key rows and value rows of 128 everywhere (a differential
+    head holds two maps of 64); the routed layers' active width (the chosen experts and the shared one) is ``ff``."""
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // (2 * top), "limit": 7.0}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": ff // 2, "limit": 7.0}}
+    dif = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 50.0, "diff": 0.6,
+           "mask": {"size": window}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 1.0, "mask": {"size": window},
+           "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    layers = []
+    for _ in range(2):
+        layers.append({"type": "attention_2", "mixer": dict(dif), "mlp": dense})
+        layers.append({"type": "attention_2", "mixer": dict(dif), "mlp": moe})
+        layers.append({"type": "attention", "mixer": dict(att), "mlp": dense})
+    return {"architecture": "Zigolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+            "loop": {"start": 1, "stop": 3, "times": times}, "layers": layers}
+
+
+PRESETS.update({
+    "zigolix-w1024": _zigolix(1024, 32768, heads=8, kv_heads=2, ff=3072, window=1024, experts=16, top=2),
+    "zigolix-w2048": _zigolix(2048, 65536, heads=16, kv_heads=4, ff=6144, window=1024, experts=16, top=2),
+})
+
+
 def preset(name: str) -> dict:
     try:
         import copy

@@ -52,6 +52,7 @@ struct AttnTcParams {
     int n_tiles, pairs;      // pairs = ceil((nq / nkv) / 2): CTAs per (tile, kv head)
     float scale_log2;
     const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
+    const float* sink;        // [nq] or null: exp(sink_h) in the softmax denominator (no key, no value)
 };
 
 // shared memory map (bytes; the tile regions are 1024-aligned)
@@ -369,6 +370,8 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         }
         if (good) {
             tc_fence_after();
+            // a sink is one more term of the denominator, against the same reference maximum as the keys' terms
+            if (p.sink && row_ok) l_run += exp2f(p.sink[head] * 1.4426950408889634f - m_ref);
             const float inv = row_ok ? 1.f / l_run : 0.f;
             bf16* orow = p.out + ((int64_t)(tok0 + row) * p.nq + head) * ATC_D;
 #pragma unroll
@@ -409,7 +412,7 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
                                           const int* page_base, int table_stride, const int* row_start,
                                           const int* row_pos, const int* tiles, int n_tiles, int nq, int nkv, int d,
                                           int P, float scale, int window, int chunk, int keep, const float* slopes,
-                                          cudaStream_t stream) {
+                                          const float* sink, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!acorn_attention_prefill_tc_supported(nq, nkv, d, P) || q_stride % 8 != 0 || ((uintptr_t)q & 15))
         return ACORN_ERR_UNSUPPORTED;
@@ -417,7 +420,7 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
     p.out = (bf16*)out; p.block_table = block_table; p.page_base = page_base; p.row_start = row_start;
     p.row_pos = row_pos; p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
     p.logP = acorn_log2_exact_tc(P); p.window = window; p.chunk = chunk; p.keep = keep; p.scale_log2 = scale * 1.4426950408889634f;
-    p.slopes = slopes;
+    p.slopes = slopes; p.sink = sink;
     p.n_tiles = n_tiles; p.pairs = (nq / nkv + 1) / 2;
     const int64_t ctas = (int64_t)n_tiles * nkv * p.pairs;
     if (ctas > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;

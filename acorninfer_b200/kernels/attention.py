@@ -131,8 +131,9 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
     take values as wide as keys; the TMA decode kernel knows windows only.  ``sink32`` (float32 [nq]): a term
     ``exp(sink_h)`` in the softmax denominator; ``softcap`` c: the scaled score becomes ``c tanh(score / c)``; ``maps``
     n > 1: every head holds n score maps side by side and ``nq`` counts (head, map) pairs (see
-    ``ops.attention_plain``).  The tcgen05 prefill kernel and the TMA decode kernel know none of the three: such
-    layers run the mma.sync prefill kernel and the cp.async split-K decode kernel."""
+    ``ops.attention_plain``).  The tcgen05 prefill kernel knows the sink alone and the TMA decode kernel none of the
+    three: capped scores and score maps run the mma.sync prefill kernel, all three the cp.async split-K decode
+    kernel."""
     if q is not None:
         qkv = q
     P = cache.k_pages.shape[2]
@@ -141,6 +142,8 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
     mask = {"chunk": chunk, "keep_first": keep_first, "slopes32": slopes32}
     if scored:
         mask.update(sink32=sink32, softcap=softcap, maps=maps)
+    tc_mask = {"chunk": chunk, "keep_first": keep_first, "slopes32": slopes32, "sink32": sink32}
+    tc_knows = not softcap and maps == 1
     if qkv.dtype == torch.bfloat16 and (value_dim is None or value_dim == d):
         if inputs.plan.all_decode and ops.attention_decode_supported(nq, nkv, d) and inputs.num_tokens <= 65535:
             bound = _key_bound(group.block_table.shape[1] * P, window, chunk, keep_first)
@@ -156,12 +159,12 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             # a mixed step: prompt portions through the prefill kernel, decoded tokens through the
             # decode kernel, both writing their rows of one output
             out = torch.empty((inputs.num_tokens, nq * d), dtype=qkv.dtype, device=qkv.device)
-            if ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0 and not scored:
+            if ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0 and tc_knows:
                 # long rows on the tcgen05 kernel (tiles of 128 queries), short ones on the mma.sync kernel
                 if hx["attention.q_tiles_large"].shape[0]:
                     ops.attention_prefill_tc(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                              group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles_large"],
-                                             inputs.num_tokens, nq, nkv, d, scale, window, out=out, **mask)
+                                             inputs.num_tokens, nq, nkv, d, scale, window, out=out, **tc_mask)
                 if hx["attention.q_tiles_small"].shape[0]:
                     ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                           group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles_small"],

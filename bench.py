@@ -13,7 +13,7 @@ the cache of the live requests) with the measured copy bandwidth.  Weights are r
 (seeded N(0, 0.02), norms 1), token ids uniform random: synthetic data.  Weights
 (15 GB) are far larger than L2, so no L2 flush is needed between steps.
 
-``--design kogonex`` (or ``vagulorn``, ``tedenex``) is another workload and prints another line: prefill and decode of that
+``--design kogonex`` (or ``vagulorn``, ``tedenex``, ``zigolix``) is another workload and prints another line: prefill and decode of that
 architecture at two sets of layer sizes beside Qwen3 dense of equal width, depth, vocabulary and active
 feed-forward width, with the device time of every kernel of one prefill and one decode step.
 """
@@ -606,7 +606,7 @@ def design_models(design: str, name: str) -> dict:
         att = next(l.mixer for l in cfg.layers if l.type == "attention")
         heads, kv_heads, ff = att.heads, att.kv_heads, cfg.layers[0].ff
     depth = len(cfg.layers)
-    if design == "tedenex":                  # a span of its layers runs several times: as deep as its layer runs
+    if design in ("tedenex", "zigolix"):     # a span of its layers runs several times: as deep as its layer runs
         from acorninfer_b200.registry import spec_for
         depth = len(spec_for(cfg).schedule)
     return {design: cfg,
@@ -642,7 +642,7 @@ def kernel_times(runner, entries_fn, torch) -> dict:
 
 
 def design_bench(args) -> int:
-    """``--design kogonex|vagulorn|tedenex``: prefill and decode of the design at layer sizes of a real model (random
+    """``--design kogonex|vagulorn|tedenex|zigolix``: prefill and decode of the design at layer sizes of a real model (random
     weights), beside Qwen3 dense of the same width, depth, vocabulary and active feed-forward width."""
     import torch
 
@@ -728,7 +728,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the batch of the headline value")
     ap.add_argument("--skip-extra", action="store_true",
                     help="leave out the per-kernel table, the continuous-batching, long-context and float32 runs")
-    ap.add_argument("--design", default=None, choices=["kogonex", "vagulorn", "tedenex"],
+    ap.add_argument("--design", default=None, choices=["kogonex", "vagulorn", "tedenex", "zigolix"],
                     help="another workload: this design at layer sizes of a real model beside Qwen3 dense at equal size")
     ap.add_argument("--design-sizes", default=None, help="with --design: comma-separated names of the size sets to run")
     args = ap.parse_args()

@@ -365,7 +365,13 @@ def _attention_case(befores, qlens, P, d, dv, nq, nkv, window, spikes, dtype, ke
         i32 = dict(dtype=torch.int32, device=DEV)
         starts = np.cumsum([0] + qlens)
         out = torch.zeros((lay["num_tokens"], nq * dv), dtype=dtype, device=DEV)
-        tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if n > 1 for q0 in range(0, n, 64)], **i32).view(-1, 2)
+        big = 32 if kernel.startswith("tc") else 10 ** 9          # rows from 32 tokens on go to the tcgen05 kernel
+        tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if n >= big for q0 in range(0, n, 128)], **i32).view(-1, 2)
+        if tiles.shape[0]:
+            assert cap is None and maps == 1
+            o.attention_prefill_tc(q_new, nq * dm, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
+                                   lay["num_tokens"], nq, nkv, d, scale, window, out=out, sink32=s32)
+        tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if 1 < n < big for q0 in range(0, n, 64)], **i32).view(-1, 2)
         if tiles.shape[0]:
             o.attention_prefill(q_new, nq * dm, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
                                 lay["num_tokens"], nq, nkv, d, scale, window, out=out, **extra)
@@ -412,6 +418,22 @@ def test_attention_window_sink_cap_and_maps(dtype, tol, kernel, d, dv, nq, nkv, 
     # key 3 of 700 decides a decoded token and a prompt's rows when nothing hides it
     got, want = _attention_case([0, 699], [40, 1], P, d, dv, nq, nkv, None, [(1, 3)], dtype, kernel, sinks, None, maps)
     assert (got - want).abs().max() < tol
+
+
+def test_sink_in_the_tcgen05_prefill_kernel():
+    """Key rows of 128: long rows on the tcgen05 kernel with a sink per head and a window, a spiked key just inside and
+    just outside it, beside short rows and decoded tokens on the other kernels."""
+    P, Wn, d, nq, nkv = 16, 40, 128, 8, 2
+    befores = [0, 100, 139, 140, 17]
+    qlens = [200, 70, 1, 1, 40]
+    spikes = [(0, 0), (0, 63), (0, 64), (0, 130), (1, 99), (1, 128), (2, 100), (3, 100), (4, 20)]
+    sinks = torch.linspace(-1.0, 3.0, nq, dtype=torch.float64)
+    got, want = _attention_case(befores, qlens, P, d, d, nq, nkv, Wn, spikes, torch.bfloat16, "tc2", sinks)
+    assert (got - want).abs().max() < 2e-2
+    none, want = _attention_case(befores, qlens, P, d, d, nq, nkv, Wn, spikes, torch.bfloat16, "tc2", None)
+    assert (none - want).abs().max() < 2e-2 and (none - got).abs().max() > 0.02
+    got, want = _attention_case([0, 300], [450, 130], P, d, d, nq, nkv, None, [(0, 3), (1, 5)], torch.bfloat16, "tc2", sinks, seed=9)
+    assert (got - want).abs().max() < 2e-2
 
 
 def test_score_maps_combined_normed_and_gated():
