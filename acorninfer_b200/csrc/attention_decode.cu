@@ -40,6 +40,7 @@ struct DecodeParams {
     const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
     const float* sink;        // [nq] or null: exp(sink_h) in the softmax denominator (no key, no value; counted by split 0)
     float scale, softcap;     // the plain scale; softcap c > 0: the scaled score becomes c tanh(score / c)
+    float cap_k, cap_log2;    // 2 scale / softcap log2(e) and softcap log2(e): see capped_score_log2
     int maps;                 // score maps side by side in a head (1: the usual head; see attention_plain.cu)
 };
 
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
                 for (int e = 0; e < 4; ++e) {
                     const int key = wkey0 + j * 8 + 2 * tq + (e & 1);
                     if (p.softcap > 0.f)
-                        s[j][e] = key < hi ? p.softcap * tanhf(s[j][e] * p.scale / p.softcap) * 1.4426950408889634f : -INFINITY;
+                        s[j][e] = key < hi ? capped_score_log2(s[j][e], p.cap_k, p.cap_log2) : -INFINITY;
                     else
                         s[j][e] = key < hi ? fmaf(s[j][e], p.scale_log2, -slope_log2[e >> 1] * (float)(pos - mask_key(key, vlo, lo)))
                                            : -INFINITY;
@@ -334,6 +335,8 @@ extern "C" int acorn_attention_decode_ex(const void* q, int64_t q_stride, void* 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes = slopes;
     p.sink = sink; p.scale = scale; p.softcap = softcap; p.maps = maps;
+    p.cap_k = softcap > 0.f ? 2.f * scale / softcap * 1.4426950408889634f : 0.f;
+    p.cap_log2 = softcap * 1.4426950408889634f;
     int rc;
     switch (d) {
         case 16: rc = launch_decode<16>(p, n, stream); break;

@@ -39,6 +39,7 @@ struct PrefillParams {
     const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
     const float* sink;        // [nq] or null
     float scale, softcap;     // the plain scale; softcap 0: none
+    float cap_k, cap_log2;    // 2 scale / softcap log2(e) and softcap log2(e): see capped_score_log2
     int maps;                 // score maps side by side in a head (1: the usual head)
 };
 
@@ -85,6 +86,13 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
                                      : 0u;
             }
         }
+    // the k-steps of 16 entries that hold this pair's map (all of them without maps, or where a map's width is no
+    // multiple of 16): the others' query entries are zero and their products are left out
+    int ks_lo = 0, ks_hi = D / 16;
+    if (p.maps > 1 && (D / p.maps) % 16 == 0) {
+        ks_lo = (head % p.maps) * (D / p.maps / 16);
+        ks_hi = ks_lo + D / p.maps / 16;
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
@@ -122,6 +130,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
             for (int j = 0; j < PRE_BN / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
+                if (ks < ks_lo || ks >= ks_hi) continue;
 #pragma unroll
                 for (int j2 = 0; j2 < PRE_BN / 16; ++j2) {
                     uint32_t b[4];
@@ -141,7 +150,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
                     const int key = mask_key(v, vlo, lo);
                     const bool ok = v < hi && mask_sees(p.mask, qp, key);
                     if (p.softcap > 0.f)
-                        s[j][e] = ok ? p.softcap * tanhf(s[j][e] * p.scale / p.softcap) * 1.4426950408889634f : -INFINITY;
+                        s[j][e] = ok ? capped_score_log2(s[j][e], p.cap_k, p.cap_log2) : -INFINITY;
                     else
                         s[j][e] = ok ? fmaf(s[j][e], p.scale_log2, -slope_log2 * (float)(qp - key)) : -INFINITY;
                     mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
@@ -243,6 +252,8 @@ extern "C" int acorn_attention_prefill(const void* q, int64_t q_stride, void* ou
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes = slopes;
     p.sink = sink; p.scale = scale; p.softcap = softcap; p.maps = maps;
+    p.cap_k = softcap > 0.f ? 2.f * scale / softcap * 1.4426950408889634f : 0.f;
+    p.cap_log2 = softcap * 1.4426950408889634f;
     switch (d) {
         case 16: return launch_prefill<16>(p, n_tiles, stream);
         case 32: return launch_prefill<32>(p, n_tiles, stream);

@@ -151,7 +151,7 @@ __device__ __forceinline__ float glu_act(float g, int act) {
 
 // the same by the fast float32 instructions (relative error about 2^-22), for results rounded to bfloat16
 template <int ACT> __device__ __forceinline__ float glu_act_fast(float g) {
-    const float z = ACT == 1 ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+    const float z = ACT == 1 ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : (ACT == 2 ? 1.702f * g : g);
     return __fdividef(g, 1.f + __expf(-z));
 }
 
@@ -179,7 +179,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 // blockIdx.y is the token, so that no index is divided by the row width; a thread takes two
 // 16-byte chunks of outputs a step (four loads in flight).
 template <int ACT>
-__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I8, int b8) {
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I8, int b8, float limit) {
     pdl_wait();
     pdl_trigger();
     const bf16* row = gu + (int64_t)blockIdx.y * I8 * 16;
@@ -189,8 +189,12 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
         uint32_t ow[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
-            const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[k]));
+            float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
+            float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[k]));
+            if (ACT == 2) {         // the capped form
+                g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
+                u.x = fminf(fmaxf(u.x, -limit), limit) + 1.f; u.y = fminf(fmaxf(u.y, -limit), limit) + 1.f;
+            }
             // exp and the quotient by the fast float32 instructions (relative error about 2^-22, far below
             // the bfloat16 rounding of the result): with the exact ones the kernel is bound by arithmetic
             __nv_bfloat162 o = __floats2bfloat162_rn(glu_act_fast<ACT>(g.x) * u.x, glu_act_fast<ACT>(g.y) * u.y);
@@ -219,15 +223,18 @@ extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int bl
     const int64_t total = (int64_t)tokens * I;
     if (total <= 0) return 0;
     if (block <= 0 || I % block != 0 || act < 0 || act > 2) return ACORN_ERR_UNSUPPORTED;
-    if (act < 2 && dtype == ACORN_DTYPE_BF16 && block % 8 == 0 && tokens <= 65535) {
+    if (dtype == ACORN_DTYPE_BF16 && block % 8 == 0 && tokens <= 65535) {
         const int I8 = I / 8;
         int bx = (I8 + 511) / 512;                  // 256 threads, two chunks each
         if (bx < 1) bx = 1;
+        if (act == 2)
+            return acorn_launch(swiglu_bf16x8_kernel<2>, dim3(bx, tokens), dim3(256), 0, stream, (const bf16*)gu,
+                                (bf16*)out, I8, block / 8, limit);
         if (act == 1)
             return acorn_launch(swiglu_bf16x8_kernel<1>, dim3(bx, tokens), dim3(256), 0, stream, (const bf16*)gu,
-                                (bf16*)out, I8, block / 8);
+                                (bf16*)out, I8, block / 8, limit);
         return acorn_launch(swiglu_bf16x8_kernel<0>, dim3(bx, tokens), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out,
-                            I8, block / 8);
+                            I8, block / 8, limit);
     }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;

@@ -55,6 +55,7 @@ struct TcParams {
     const float* ss_in;      // [ss_parts, M] or nullptr
     int ss_parts, norm_width;
     float eps;
+    float glu_limit;         // TC_MODE_SWIGLU_PAIRS: > 0: the capped form, g = min(gate, L), u = clamp(up, -L, L), g sigmoid(1.702 g) (u + 1)
     // TC_MODE_ADD_NORM
     float* resid;            // [M, ldr] float32, updated in place
     int64_t ldr;
@@ -344,9 +345,15 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         // gate and up columns in turns: the thread of an even column takes both
         for (int i = 0, m = rank; m < m_valid; ++i, m += csize) {
             if ((col & 1) == 0 && n0 + col + 1 < p.N) {
-                const float g = tile_sum(i, col) * inv_s[m], u = tile_sum(i, col + 1) * inv_s[m];
+                float g = tile_sum(i, col) * inv_s[m], u = tile_sum(i, col + 1) * inv_s[m];
+                float z = g;
+                if (p.glu_limit > 0.f) {
+                    g = fminf(g, p.glu_limit);
+                    u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit) + 1.f;
+                    z = 1.702f * g;
+                }
                 reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + ((n0 + col) >> 1)] =
-                    __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                    __float2bfloat16_rn(g / (1.f + expf(-z)) * u);
             }
         }
     } else if (p.mode == TC_MODE_QKV_ROPE) {
@@ -553,10 +560,11 @@ extern "C" int acorn_gemm_tc_qkv_rope(const void* x, int64_t ldx, const void* w,
 
 // A product per expert on tiles of 128 rows: x [slots, K] holds every expert's rows together (offsets [E + 1]),
 // w [E, N, K] contiguous, out [slots, N] or, with swiglu_pairs (weight rows 2i / 2i + 1 = gate / up of output i),
-// silu(gate) * up [slots, N / 2].  Rows beyond an expert's last one in its last tile are computed and not stored.
+// silu(gate) * up [slots, N / 2] (glu_limit L > 0: the capped form min(gate, L) sigmoid(1.702 min(gate, L)) (clamp(up, -L, L) + 1)).
+// Rows beyond an expert's last one in its last tile are computed and not stored.
 extern "C" int acorn_grouped_gemm_tcgen05(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo,
                                           const int* offsets, int slots, int E, int N, int K, int swiglu_pairs,
-                                          cudaStream_t stream) {
+                                          float glu_limit, cudaStream_t stream) {
     if (slots <= 0 || E <= 0 || N <= 0) return 0;
     if (!acorn_gemm_tc_supported(slots, N, K, ldx, K) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACORN_ERR_UNSUPPORTED;
     if (swiglu_pairs && N % 2) return ACORN_ERR_UNSUPPORTED;
@@ -565,6 +573,7 @@ extern "C" int acorn_grouped_gemm_tcgen05(const void* x, int64_t ldx, const void
     TcParams p = {};
     p.out = out; p.ldo = ldo; p.M = slots; p.N = N; p.K = K; p.out_f32 = 0;
     p.mode = swiglu_pairs ? TC_MODE_SWIGLU_PAIRS : TC_MODE_PLAIN;
+    p.glu_limit = glu_limit;
     p.g_offsets = offsets; p.g_experts = E; p.g_tiles = (int)tiles;
     p.kblocks = (K + TC_BK - 1) / TC_BK;
     CUtensorMap mw, mx;

@@ -285,7 +285,8 @@ template <int BM>
 __global__ void __launch_bounds__(256) grouped_gemm_tc_kernel(const bf16* __restrict__ A, int64_t lda,
                                                               const int* __restrict__ a_rows, const bf16* __restrict__ W,
                                                               bf16* __restrict__ C, int64_t ldc,
-                                                              const int* __restrict__ offsets, int E, int N, int K, int swiglu) {
+                                                              const int* __restrict__ offsets, int E, int N, int K, int swiglu,
+                                                              float glu_limit) {
     extern __shared__ __align__(16) unsigned char gt_smem[];
     bf16* sA = reinterpret_cast<bf16*>(gt_smem);                               // [STAGES][BM][LDS]
     bf16* sW = sA + GT_STAGES * BM * GT_LDS;                                   // [STAGES][BN][LDS]
@@ -394,7 +395,13 @@ __global__ void __launch_bounds__(256) grouped_gemm_tc_kernel(const bf16* __rest
                 const float v0 = acc[mt][nt][half * 2], v1 = acc[mt][nt][half * 2 + 1];
                 if (swiglu) {
                     // weight rows 2i and 2i + 1 are the gate and the up row of output i: both are this thread's
-                    if (n + 1 < N) C[(int64_t)slot * ldc + (n >> 1)] = __float2bfloat16_rn(v0 / (1.f + expf(-v0)) * v1);
+                    float g = v0, u = v1, z = v0;
+                    if (glu_limit > 0.f) {      // the capped form
+                        g = fminf(g, glu_limit);
+                        u = fminf(fmaxf(u, -glu_limit), glu_limit) + 1.f;
+                        z = 1.702f * g;
+                    }
+                    if (n + 1 < N) C[(int64_t)slot * ldc + (n >> 1)] = __float2bfloat16_rn(g / (1.f + expf(-z)) * u);
                     continue;
                 }
                 if (n + 1 < N && (ldc & 1) == 0) {
@@ -410,7 +417,8 @@ __global__ void __launch_bounds__(256) grouped_gemm_tc_kernel(const bf16* __rest
 
 template <int BM>
 static int grouped_gemm_tc_launch(const bf16* A, int64_t lda, const int* a_rows, const bf16* W, bf16* C, int64_t ldc,
-                                  const int* offsets, int slots, int E, int N, int K, int swiglu, cudaStream_t stream) {
+                                  const int* offsets, int slots, int E, int N, int K, int swiglu, float glu_limit,
+                                  cudaStream_t stream) {
     const int64_t tiles = (slots + BM - 1) / BM + E;
     if (tiles > 65535) return ACORN_ERR_UNSUPPORTED;
     const size_t smem = (size_t)GT_STAGES * (BM + GT_BN) * GT_LDS * sizeof(bf16);
@@ -421,7 +429,7 @@ static int grouped_gemm_tc_launch(const bf16* A, int64_t lda, const int* a_rows,
         configured.mark();
     }
     dim3 grid((N + GT_BN - 1) / GT_BN, (unsigned)tiles);
-    return acorn_launch(grouped_gemm_tc_kernel<BM>, grid, dim3(256), smem, stream, A, lda, a_rows, W, C, ldc, offsets, E, N, K, swiglu);
+    return acorn_launch(grouped_gemm_tc_kernel<BM>, grid, dim3(256), smem, stream, A, lda, a_rows, W, C, ldc, offsets, E, N, K, swiglu, glu_limit);
 }
 
 extern "C" int acorn_grouped_gemm_fuses_swiglu(int N, int K, int64_t lda, int dtype) {
@@ -429,9 +437,10 @@ extern "C" int acorn_grouped_gemm_fuses_swiglu(int N, int K, int64_t lda, int dt
 }
 
 // swiglu: W holds, per output i, the gate row 2i and the up row 2i + 1; C [slots, N / 2] receives
-// silu(gate) * up computed from the float32 sums (tensor-core kernel only: see the query above).
+// silu(gate) * up computed from the float32 sums (tensor-core kernel only: see the query above); glu_limit L > 0:
+// the capped form min(gate, L) sigmoid(1.702 min(gate, L)) (clamp(up, -L, L) + 1).
 extern "C" int acorn_grouped_gemm(const void* A, int64_t lda, const int* a_rows, const void* W, void* C, int64_t ldc,
-                                  const int* offsets, int slots, int E, int N, int K, int dtype, int swiglu,
+                                  const int* offsets, int slots, int E, int N, int K, int dtype, int swiglu, float glu_limit,
                                   cudaStream_t stream) {
     if (slots <= 0 || E <= 0 || N <= 0) return 0;
     if (swiglu && !(acorn_grouped_gemm_fuses_swiglu(N, K, lda, dtype) && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0))
@@ -439,10 +448,10 @@ extern "C" int acorn_grouped_gemm(const void* A, int64_t lda, const int* a_rows,
     if (dtype == ACORN_DTYPE_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
         // few rows an expert on average: the small tile (a decode step); else the large one
         if ((int64_t)slots <= (int64_t)16 * E)
-            return grouped_gemm_tc_launch<16>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, stream);
+            return grouped_gemm_tc_launch<16>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, glu_limit, stream);
         if ((int64_t)slots >= (int64_t)256 * E)          // several full tiles an expert: the tall tile (64 x 32 a warp)
-            return grouped_gemm_tc_launch<128>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, stream);
-        return grouped_gemm_tc_launch<64>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, stream);
+            return grouped_gemm_tc_launch<128>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, glu_limit, stream);
+        return grouped_gemm_tc_launch<64>((const bf16*)A, lda, a_rows, (const bf16*)W, (bf16*)C, ldc, offsets, slots, E, N, K, swiglu, glu_limit, stream);
     }
     const int64_t tiles = (slots + GG_BM - 1) / GG_BM + E;       // every expert may end in a partly filled tile
     if (tiles > 65535) return ACORN_ERR_UNSUPPORTED;

@@ -145,10 +145,10 @@ class _Sigs:
     acorn_moe_route = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     acorn_moe_plan = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_grouped_gemm = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
-                          c_int, c_int, c_int, c_void_p]
+                          c_int, c_int, c_int, c_float, c_void_p]
     acorn_grouped_gemm_fuses_swiglu = [c_int, c_int, c_int64, c_int]
     acorn_grouped_gemm_tcgen05 = [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                  c_void_p]
+                                  c_float, c_void_p]
     acorn_gather_rows = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                          c_void_p, c_void_p, c_float, c_void_p, c_void_p]
@@ -1796,12 +1796,15 @@ GROUPED_TCGEN05_MIN_ROWS = 64      # rows an expert on average from which the gr
 
 
 def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, offsets: torch.Tensor, slots: int,
-                 swiglu_pairs: bool = False) -> torch.Tensor:
+                 swiglu_pairs: bool = False, activation: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """out[slot] = a[a_rows[slot]] @ w[e]^T for the slots offsets[e] .. offsets[e + 1] - 1 of every
     expert e (w [E, N, K]); rows of other slots are left unwritten.  ``swiglu_pairs``: rows 2i and 2i + 1 of
     ``w[e]`` are the gate and the up row of output i, and what is returned is ``silu(gate) * up``
     [slots, N / 2]: inside the product's epilogue on the tensor-core kernel, by the SwiGLU kernel after it
-    otherwise."""
+    otherwise.  ``activation="capped_swish"`` with ``limit`` L: the capped form instead of silu (see ``swiglu``)."""
+    if activation not in ("silu", "capped_swish") or (activation == "capped_swish" and not limit > 0):
+        raise KernelError(f"grouped_gemm: activation {activation!r} with limit {limit}")
+    glu_limit = float(limit) if activation == "capped_swish" else 0.0
     _check(a, "a", None, 2)
     _check(w, "w", a.dtype, 3)
     E, N, K = w.shape
@@ -1821,15 +1824,15 @@ def grouped_gemm(a: torch.Tensor, a_rows: torch.Tensor | None, w: torch.Tensor, 
             rows_in = a
         out = torch.empty((slots, N // 2 if swiglu_pairs else N), dtype=a.dtype, device=a.device)
         _ok(lib().acorn_grouped_gemm_tcgen05(rows_in.data_ptr(), rows_in.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
-                                             offsets.data_ptr(), slots, E, N, K, 1 if swiglu_pairs else 0, _stream()),
+                                             offsets.data_ptr(), slots, E, N, K, 1 if swiglu_pairs else 0, glu_limit, _stream()),
             "grouped_gemm_tcgen05", f"{slots}x{N}x{K}")
         return out
     out = torch.empty((slots, N // 2 if fused else N), dtype=a.dtype, device=a.device)
     _ok(lib().acorn_grouped_gemm(a.data_ptr(), a.stride(0), _ptr(a_rows), w.data_ptr(), out.data_ptr(), out.stride(0),
-                                 offsets.data_ptr(), slots, E, N, K, dtype_code(a.dtype), 1 if fused else 0, _stream()),
+                                 offsets.data_ptr(), slots, E, N, K, dtype_code(a.dtype), 1 if fused else 0, glu_limit, _stream()),
         "grouped_gemm", f"{slots}x{N}x{K}")
     if swiglu_pairs and not fused:
-        return swiglu(out, block=1)
+        return swiglu(out, block=1, activation=activation, limit=limit)
     return out
 
 

@@ -98,11 +98,8 @@ class RoutedExperts(FeedForward):
         if self.E:
             w_gu = self.w_gate_up if self.w_gate_up.dtype == x.dtype else self.w_gate_up.to(x.dtype)
             w_dn = self.w_down if self.w_down.dtype == x.dtype else self.w_down.to(x.dtype)
-            if self.activation == "silu":
-                hidden = ops.grouped_gemm(x, slot_token, w_gu, offsets, slots, swiglu_pairs=True)
-            else:       # gate and up rows in turns: blocks of one
-                hidden = ops.swiglu(ops.grouped_gemm(x, slot_token, w_gu, offsets, slots), block=1,
-                                    activation=self.activation, limit=self.limit)
+            hidden = ops.grouped_gemm(x, slot_token, w_gu, offsets, slots, swiglu_pairs=True, activation=self.activation,
+                                      limit=self.limit)
             y = ops.grouped_gemm(hidden, None, w_dn, offsets, slots)
         else:
             y = x
