@@ -53,6 +53,7 @@ struct AttnTcParams {
     float scale_log2;
     const float* slopes;      // [nq] or null: slope_h * (query position - key position) is taken off the score
     const float* sink;        // [nq] or null: exp(sink_h) in the softmax denominator (no key, no value)
+    float cap_k, cap_c2;      // a cap c on the scaled scores: 2 scale / c log2(e) and c / scale (cap_c2 0: none)
 };
 
 // shared memory map (bytes; the tile regions are 1024-aligned)
@@ -71,6 +72,13 @@ template <int C0>
 __device__ __forceinline__ void atc_distance(float (&s)[64], float step) {
 #pragma unroll
     for (int c = 0; c < 64; ++c) s[c] = fmaf(step, (float)(C0 + c), s[c]);
+}
+
+// s[c] <- (cap / scale) tanh(s[c] scale / cap): the capped score in units of the raw one, tanh(z) = 1 - 2 / (1 + e^(2z))
+// by the fast exponential and quotient (two more special-function operations a score beside the softmax's own)
+__device__ __forceinline__ void atc_cap(float (&s)[64], float k, float c2) {
+#pragma unroll
+    for (int c = 0; c < 64; ++c) s[c] = c2 * (1.f - __fdividef(2.f, 1.f + fast_exp2(s[c] * k)));
 }
 
 // -inf where the query at qpos may not see the key (causal, the first key its window or its block of positions
@@ -300,6 +308,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         float m_ref = -INFINITY, l_run = 0.f;
         const float dist_step = p.slopes ? p.slopes[head] * 1.4426950408889634f / p.scale_log2 : 0.f;
         const bool sloped = p.slopes != nullptr;
+        const bool capped = p.cap_c2 > 0.f;
         bool good = true;
         for (int j = 0; j < nb; ++j) {
             // S of block j is complete; so is P V of block j-1, issued before it: O is stable
@@ -309,7 +318,9 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             tc_fence_after();
             const int key0 = ATC_KEY0(j);
             // a block every query of the tile sees whole needs no mask
-            const bool masked = key0 + ATC_BN - 1 > pos0 || p.window > 0 || p.chunk > 0 || p.keep > 0 || n_q < ATC_BM;
+            // (under a window: the block's first key lies inside the window of the tile's last query, whose window starts last)
+            const bool masked = key0 + ATC_BN - 1 > pos0 || (p.window > 0 && key0 < pos0 + n_q - p.window) || p.chunk > 0 ||
+                                p.keep > 0 || n_q < ATC_BM;
             // One pass in the common case: exponentiate against the reference maximum the row
             // already has while the block's own maximum is taken; only a row whose maximum
             // outgrew the reference by more than 2^8 (always so in its first block) moves the
@@ -320,11 +331,13 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             const float off = sloped ? -dist_step * (float)(qpos - key0) : 0.f, off2 = off * p.scale_log2;
             float neg_ref = (m_ref == -INFINITY ? 0.f : -m_ref) + off2;
             tmem_ld64(my_s, s);
+            if (capped) atc_cap(s, p.cap_k, p.cap_c2);
             if (sloped) atc_distance<0>(s, dist_step);
             if (masked) atc_mask(s, key0, qpos, row_ok, first_seen, p.keep);
             float mx = atc_max(s);
             float psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             tmem_ld64(my_s + 64, s);
+            if (capped) atc_cap(s, p.cap_k, p.cap_c2);
             if (sloped) atc_distance<64>(s, dist_step);
             if (masked) atc_mask(s, key0 + 64, qpos, row_ok, first_seen, p.keep);
             mx = (fmaxf(mx, atc_max(s)) + off) * p.scale_log2;           // the scale is positive
@@ -339,6 +352,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
                 }
                 psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
                 tmem_ld64(my_s, s);
+                if (capped) atc_cap(s, p.cap_k, p.cap_c2);
                 if (sloped) atc_distance<0>(s, dist_step);
                 if (masked) atc_mask(s, key0, qpos, row_ok, first_seen, p.keep);
                 psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
@@ -412,7 +426,7 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
                                           const int* page_base, int table_stride, const int* row_start,
                                           const int* row_pos, const int* tiles, int n_tiles, int nq, int nkv, int d,
                                           int P, float scale, int window, int chunk, int keep, const float* slopes,
-                                          const float* sink, cudaStream_t stream) {
+                                          const float* sink, float softcap, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!acorn_attention_prefill_tc_supported(nq, nkv, d, P) || q_stride % 8 != 0 || ((uintptr_t)q & 15))
         return ACORN_ERR_UNSUPPORTED;
@@ -421,6 +435,9 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
     p.row_pos = row_pos; p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
     p.logP = acorn_log2_exact_tc(P); p.window = window; p.chunk = chunk; p.keep = keep; p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes = slopes; p.sink = sink;
+    if (softcap < 0.f || (softcap > 0.f && (slopes != nullptr || !(scale > 0.f)))) return ACORN_ERR_UNSUPPORTED;
+    p.cap_k = softcap > 0.f ? 2.f * scale / softcap * 1.4426950408889634f : 0.f;
+    p.cap_c2 = softcap > 0.f ? softcap / scale : 0.f;
     p.n_tiles = n_tiles; p.pairs = (nq / nkv + 1) / 2;
     const int64_t ctas = (int64_t)n_tiles * nkv * p.pairs;
     if (ctas > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;

@@ -131,9 +131,9 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
     take values as wide as keys; the TMA decode kernel knows windows only.  ``sink32`` (float32 [nq]): a term
     ``exp(sink_h)`` in the softmax denominator; ``softcap`` c: the scaled score becomes ``c tanh(score / c)``; ``maps``
     n > 1: every head holds n score maps side by side and ``nq`` counts (head, map) pairs (see
-    ``ops.attention_plain``).  The tcgen05 prefill kernel knows the sink alone and the TMA decode kernel none of the
-    three: capped scores and score maps run the mma.sync prefill kernel, all three the cp.async split-K decode
-    kernel."""
+    ``ops.attention_plain``).  The tcgen05 prefill kernel knows the sink and the cap and the TMA decode kernel none
+    of the three: score maps run the mma.sync prefill kernel (unless the caller lays the pairs' queries out with
+    zeros itself and passes ``maps`` 1), all three the cp.async split-K decode kernel."""
     if q is not None:
         qkv = q
     P = cache.k_pages.shape[2]
@@ -142,8 +142,8 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
     mask = {"chunk": chunk, "keep_first": keep_first, "slopes32": slopes32}
     if scored:
         mask.update(sink32=sink32, softcap=softcap, maps=maps)
-    tc_mask = {"chunk": chunk, "keep_first": keep_first, "slopes32": slopes32, "sink32": sink32}
-    tc_knows = not softcap and maps == 1
+    tc_mask = {"chunk": chunk, "keep_first": keep_first, "slopes32": slopes32, "sink32": sink32, "softcap": softcap}
+    tc_knows = maps == 1 and not (softcap and slopes32 is not None) and scale > 0
     if qkv.dtype == torch.bfloat16 and (value_dim is None or value_dim == d):
         if inputs.plan.all_decode and ops.attention_decode_supported(nq, nkv, d) and inputs.num_tokens <= 65535:
             bound = _key_bound(group.block_table.shape[1] * P, window, chunk, keep_first)

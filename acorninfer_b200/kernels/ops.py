@@ -178,7 +178,7 @@ class _Sigs:
                      c_void_p]
     acorn_attention_prefill_tc = [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                  c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+                                  c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p]
     acorn_attention_prefill_tc_supported = [c_int, c_int, c_int, c_int]
     acorn_attention_tc_error = []
     acorn_gemm_tc_ex = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
@@ -703,7 +703,8 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, 
                          row_pos: torch.Tensor, tiles: torch.Tensor, num_tokens: int, num_heads: int,
                          num_kv_heads: int, head_dim: int, scale: float, window: int | None,
                          out: torch.Tensor | None = None, chunk: int | None = None, keep_first: int = 0,
-                         slopes32: torch.Tensor | None = None, sink32: torch.Tensor | None = None) -> torch.Tensor:
+                         slopes32: torch.Tensor | None = None, sink32: torch.Tensor | None = None,
+                         softcap: float | None = None) -> torch.Tensor:
     """tcgen05/TMA prefill attention (bfloat16, head size 128) for the query tiles listed in
     ``tiles`` (int32 [n, 2]: row, first token within the row; 128 tokens a tile at most).  CTAs
     start in the order of the list: give the tiles that read the most keys first."""
@@ -711,8 +712,10 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, 
         raise KernelError("attention_prefill_tc takes bfloat16")
     _check_slopes(slopes32, num_heads)
     _check_sink(sink32, num_heads)
-    if slopes32 is not None and not scale > 0:
-        raise KernelError("attention_prefill_tc: slopes need a positive scale")
+    if (slopes32 is not None or softcap) and not scale > 0:
+        raise KernelError("attention_prefill_tc: slopes and a cap need a positive scale")
+    if slopes32 is not None and softcap:
+        raise KernelError("attention_prefill_tc: a cap does not go with a distance penalty")
     _check(k_pages, "k_pages", q.dtype, 4)
     _check(v_pages, "v_pages", q.dtype, 4)
     if not attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim, k_pages.shape[2]):
@@ -729,7 +732,8 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, 
                                          page_base.data_ptr(), block_table.stride(0), row_start.data_ptr(),
                                          row_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], num_heads,
                                          num_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window or 0),
-                                         int(chunk or 0), int(keep_first or 0), _ptr(slopes32), _ptr(sink32), _stream()),
+                                         int(chunk or 0), int(keep_first or 0), _ptr(slopes32), _ptr(sink32),
+                                         float(softcap or 0.0), _stream()),
         "attention_prefill_tc")
     return out
 

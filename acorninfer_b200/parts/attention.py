@@ -163,7 +163,8 @@ class Attention(Mixer):
         return attn_kernels.STEP_ARRAYS
 
     def fusable(self, num_rows):
-        return (self.plain and self._rows_fuse(num_rows) and self.w_qkv.dtype == torch.bfloat16
+        # (the options only change what runs between the two products, which take the fused forms either way)
+        return (self._rows_fuse(num_rows) and self.w_qkv.dtype == torch.bfloat16
                 and self.w_o.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and (self.nq * self.d) % 8 == 0)
 
     def _rows_fuse(self, num_rows):

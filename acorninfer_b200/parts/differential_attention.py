@@ -16,6 +16,11 @@ and writes k and v into the pages (a key head is a row of ``2 dim``); the attent
 (head, map) pairs as heads of their own over key rows of ``2 dim`` (a pair is scored against its map's half of
 the key row), which gives a1 and a2 side by side; one kernel forms ``o``, norms and gates it; the output product
 follows.  ``lambda`` is evaluated once, in float64, when the weights are bound.
+
+Key rows of 128 under bfloat16 (``spread``): the query matrix is bound with a pair's rows laid out over the whole
+key row, zeros outside its map's half, so that the product itself yields the pairs' queries as heads of 128 and
+the tcgen05 prefill kernel, which takes its queries by TMA, serves the layer (the query product doubles: about a
+fortieth of a layer's multiply-adds at these sizes).
 """
 
 from __future__ import annotations
@@ -35,6 +40,7 @@ _NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "gate": "g", "q_bias": "q.b", 
 @MIXERS.register("differential_attention")
 class DifferentialAttention(Mixer):
     graph_safe = True
+    supports_epilogue = True
     adds_residual = True
 
     def __init__(self, ctx: BuildContext, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, value_dim: int,
@@ -51,9 +57,11 @@ class DifferentialAttention(Mixer):
         self.scale, self.diff, self.eps, self.softcap, self.window = float(scale), float(diff), float(norm_eps), softcap, window
         self.bias = bool(bias)
         self.names = {**_NAMES, **(names or {})}
-        self.channels = (self.H + self.G) * 2 * dim + self.G * value_dim          # q, k, v columns of a projected row
         self.w_in = self.w_o = self.bias32 = None
         self.lam = None
+        # the pairs' queries laid out over the whole key row by the product itself: where the tcgen05 kernel can take them
+        self.spread = ctx.dtype == torch.bfloat16 and 2 * dim == 128 and value_dim == 128
+        self.q_cols = (2 if self.spread else 1) * self.H * 2 * dim
 
     def tensor_specs(self):
         n, W = self.names, self.hidden_size
@@ -72,12 +80,26 @@ class DifferentialAttention(Mixer):
         n = self.names
         parts = [tensors[n[w]] for w in ("q", "k", "v", "gate")]
         dtype = parts[0].dtype if all(p.dtype == parts[0].dtype for p in parts) else torch.float32
+        biases = [tensors[n[w + "_bias"]].to(torch.float32) for w in ("q", "k", "v")] if self.bias else None
+        if self.spread:
+            parts[0] = self._spread_rows(parts[0])
+            if biases:
+                biases[0] = self._spread_rows(biases[0])
         self.w_in = torch.cat([p.to(dtype) for p in parts], dim=0).contiguous()
         self.w_o = tensors[n["o"]].contiguous()
-        if self.bias:
-            self.bias32 = torch.cat([tensors[n[w + "_bias"]].to(torch.float32) for w in ("q", "k", "v")]).contiguous()
+        if biases:
+            self.bias32 = torch.cat(biases).contiguous()
         l64 = {w: tensors[n[w]].to(torch.float64).cpu() for w in ("lq1", "lk1", "lq2", "lk2")}
         self.lam = math.exp(float((l64["lq1"] * l64["lk1"]).sum())) - math.exp(float((l64["lq2"] * l64["lk2"]).sum())) + self.diff
+
+    def _spread_rows(self, t):
+        """Rows [H, 2, dim] of a query tensor as [H, 2, 2 dim]: pair (h, a) keeps its rows at a dim .. and zeros elsewhere."""
+        d = self.d
+        src = t.reshape(self.H, 2, d, *t.shape[1:])
+        out = src.new_zeros((self.H, 2, 2 * d, *t.shape[1:]))
+        for a in range(2):
+            out[:, a, a * d:(a + 1) * d] = src[:, a]
+        return out.reshape(self.H * 2 * 2 * d, *t.shape[1:])
 
     def cache_needs(self):
         return CacheNeeds(kv=KVNeeds(self.G, 2 * self.d, self.window, value_dim=None if self.dv == 2 * self.d else self.dv))
@@ -85,21 +107,30 @@ class DifferentialAttention(Mixer):
     def step_arrays(self):
         return attn_kernels.STEP_ARRAYS
 
-    def forward(self, x, inputs, cache, residual32=None):
+    def fusable(self, num_rows):
+        widths = (self.w_in.shape[0], self.hidden_size)                         # of the first and of the output product
+        return (ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
+                and self.w_in.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16
+                and self.hidden_size % 8 == 0 and (self.H * self.dv) % 8 == 0)
+
+    def forward(self, x, inputs, cache, epilogue=None, residual32=None):
         if not cache.write:
             raise ValueError("differential attention keeps a cache of its own")
         g = inputs.groups[cache.group]
         D = 2 * self.d
         proj = ops.linear(x, self.w_in, out_dtype=self.ctx.dtype)
-        q = torch.empty((proj.shape[0], self.H * D), dtype=self.ctx.dtype, device=proj.device)
+        nq = 2 * self.H if self.spread else self.H          # query heads of a key row's width in a projected row
+        q = torch.empty((proj.shape[0], nq * D), dtype=self.ctx.dtype, device=proj.device)
         ops.qk_rope_kv(proj, None, None, _no_freq(self.ctx.device), inputs.positions, inputs.token_row, g.block_table,
-                       g.page_base, cache.k_pages, cache.v_pages, self.H, self.G, D, 0, False, 0.0, write_kv=True,
+                       g.page_base, cache.k_pages, cache.v_pages, nq, self.G, D, 0, False, 0.0, write_kv=True,
                        value_dim=self.dv, bias32=self.bias32, q_out=q)
         # the 2 H (head, map) pairs as heads over key rows of 2 dim: a1 and a2 of every head side by side
         pairs = attn_kernels.paged_attention(q, inputs, g, cache, 2 * self.H, self.G, D, self.scale, self.window,
-                                             value_dim=self.dv, softcap=self.softcap, maps=2)
-        o = ops.diff_combine(pairs, proj[:, self.channels:], self.H, self.dv, self.lam, 1.0 - self.diff, self.eps)
-        return ops.linear(o, self.w_o, out_dtype=self.ctx.dtype, residual32=residual32)
+                                             value_dim=self.dv, softcap=self.softcap, maps=1 if self.spread else 2)
+        gate_col = self.q_cols + self.G * (D + self.dv)
+        o = ops.diff_combine(pairs, proj[:, gate_col:], self.H, self.dv, self.lam, 1.0 - self.diff, self.eps)
+        return ops.linear(o, self.w_o, out_dtype=self.ctx.dtype, epilogue=epilogue,
+                          residual32=residual32 if epilogue is None else None)
 
 
 _NO_FREQ: dict = {}

@@ -368,9 +368,9 @@ def _attention_case(befores, qlens, P, d, dv, nq, nkv, window, spikes, dtype, ke
         big = 32 if kernel.startswith("tc") else 10 ** 9          # rows from 32 tokens on go to the tcgen05 kernel
         tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if n >= big for q0 in range(0, n, 128)], **i32).view(-1, 2)
         if tiles.shape[0]:
-            assert cap is None and maps == 1
+            assert maps == 1
             o.attention_prefill_tc(q_new, nq * dm, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
-                                   lay["num_tokens"], nq, nkv, d, scale, window, out=out, sink32=s32)
+                                   lay["num_tokens"], nq, nkv, d, scale, window, out=out, sink32=s32, softcap=cap)
         tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) if 1 < n < big for q0 in range(0, n, 64)], **i32).view(-1, 2)
         if tiles.shape[0]:
             o.attention_prefill(q_new, nq * dm, *common, torch.tensor(starts, **i32), torch.tensor(befores, **i32), tiles,
@@ -420,9 +420,9 @@ def test_attention_window_sink_cap_and_maps(dtype, tol, kernel, d, dv, nq, nkv, 
     assert (got - want).abs().max() < tol
 
 
-def test_sink_in_the_tcgen05_prefill_kernel():
-    """Key rows of 128: long rows on the tcgen05 kernel with a sink per head and a window, a spiked key just inside and
-    just outside it, beside short rows and decoded tokens on the other kernels."""
+def test_sink_and_cap_in_the_tcgen05_prefill_kernel():
+    """Key rows of 128: long rows on the tcgen05 kernel with a sink per head, capped scores and a window, a spiked key
+    just inside and just outside it, beside short rows and decoded tokens on the other kernels."""
     P, Wn, d, nq, nkv = 16, 40, 128, 8, 2
     befores = [0, 100, 139, 140, 17]
     qlens = [200, 70, 1, 1, 40]
@@ -430,10 +430,17 @@ def test_sink_in_the_tcgen05_prefill_kernel():
     sinks = torch.linspace(-1.0, 3.0, nq, dtype=torch.float64)
     got, want = _attention_case(befores, qlens, P, d, d, nq, nkv, Wn, spikes, torch.bfloat16, "tc2", sinks)
     assert (got - want).abs().max() < 2e-2
+    got0 = got
     none, want = _attention_case(befores, qlens, P, d, d, nq, nkv, Wn, spikes, torch.bfloat16, "tc2", None)
     assert (none - want).abs().max() < 2e-2 and (none - got).abs().max() > 0.02
     got, want = _attention_case([0, 300], [450, 130], P, d, d, nq, nkv, None, [(0, 3), (1, 5)], torch.bfloat16, "tc2", sinks, seed=9)
     assert (got - want).abs().max() < 2e-2
+    for sk, cp in ((None, 30.0), (sinks, 1.5), (sinks, 8.0)):
+        capped, want = _attention_case(befores, qlens, P, d, d, nq, nkv, Wn, spikes, torch.bfloat16, "tc2", sk, cp)
+        assert (capped - want).abs().max() < 2e-2, (sk is None, cp)
+        assert (capped - (none if sk is None else got0)).abs().max() > 0.02
+    capped, want = _attention_case([0, 300], [450, 130], P, d, d, nq, nkv, None, [(0, 3), (1, 5)], torch.bfloat16, "tc2", None, 4.0, seed=9)
+    assert (capped - want).abs().max() < 2e-2
 
 
 def test_score_maps_combined_normed_and_gated():

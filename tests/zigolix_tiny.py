@@ -60,7 +60,7 @@ ZIG_C = dict(page_size=16, seed=33, cfg=ZigolixConfig(
         L(dif(heads=4, kv_heads=2, dim=32, vdim=64, scale=0.18, diff=0.6, softcap=20.0, mask=40), ff=192),
         L(sink(heads=4, kv_heads=2, dim=64, scale=0.3, mask=50, rot=32, base=5e4, scaling=RotaryScaling(2.0, 128, 16.0, 1.0)),
           ff=moe(64, 2.0, 8, 2, 64, 2.0)),
-        L(dif(heads=2, kv_heads=1, dim=64, vdim=128, scale=0.12, diff=0.4, softcap=None, mask=100), ff=moe(32, 1.0, 6, 3)),
+        L(dif(heads=2, kv_heads=1, dim=64, vdim=128, scale=0.12, diff=0.4, softcap=6.0, mask=100), ff=moe(32, 1.0, 6, 3)),
         L(sink(heads=8, kv_heads=1, dim=32, scale=0.4, mask=None, rot=32, base=1e4), ff=64),
     )))
 
