@@ -718,12 +718,61 @@ __global__ void diff_combine_kernel(const T* __restrict__ a, const T* __restrict
     }
 }
 
+// The same for value rows that are multiples of four up to 512 with aligned rows: four entries a lane (8- or 16-byte
+// accesses), the lane's part of the row in registers between the sum of squares and the write.
+template <typename T>
+__global__ void diff_combine_vec_kernel(const T* __restrict__ a, const T* __restrict__ g, int64_t ldg, T* __restrict__ out,
+                                        int64_t items, int heads, int dv, float lambda, float scale, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int64_t t = item / heads;
+    const int h = (int)(item - t * heads);
+    const T* a1 = a + item * 2 * dv;
+    const T* a2 = a1 + dv;
+    float4 o[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = (u * 32 + lane) * 4;
+        o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < dv) {
+            const float4 x = Vec4<T>::load(a1 + i), y = Vec4<T>::load(a2 + i);
+            o[u] = make_float4(x.x - lambda * y.x, x.y - lambda * y.y, x.z - lambda * y.z, x.w - lambda * y.w);
+            ss += o[u].x * o[u].x + o[u].y * o[u].y + o[u].z * o[u].z + o[u].w * o[u].w;
+        }
+    }
+    ss = warp_sum(ss);
+    const float f = rsqrtf(ss / (float)dv + eps) * scale;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = (u * 32 + lane) * 4;
+        if (i < dv) {
+            float4 r = make_float4(o[u].x * f, o[u].y * f, o[u].z * f, o[u].w * f);
+            if (g) {
+                const float4 z = Vec4<T>::load(g + t * ldg + (int64_t)h * dv + i);
+                r.x /= 1.f + expf(-z.x); r.y /= 1.f + expf(-z.y); r.z /= 1.f + expf(-z.z); r.w /= 1.f + expf(-z.w);
+            }
+            Vec4<T>::store(out + item * dv + i, r);
+        }
+    }
+}
+
 extern "C" int acorn_diff_combine(const void* a, const void* g, int64_t ldg, void* out, int tokens, int heads, int dv,
                                   float lambda, float scale, float eps, int dtype, cudaStream_t stream) {
     const int64_t items = (int64_t)tokens * heads;
     if (items <= 0) return 0;
     if (dv < 1) return ACORN_ERR_UNSUPPORTED;
     const int warps = 8;
+    const uintptr_t align = dtype == ACORN_DTYPE_F32 ? 15 : 7;
+    if (dv % 4 == 0 && dv <= 512 && ldg % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out)) & align) == 0) {
+        ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(diff_combine_vec_kernel<T>, dim3((unsigned)((items + warps - 1) / warps)),
+                                                           dim3(32 * warps), 0, stream, (const T*)a, (const T*)g, ldg, (T*)out,
+                                                           items, heads, dv, lambda, scale, eps));
+    }
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(diff_combine_kernel<T>, dim3((unsigned)((items + warps - 1) / warps)),
                                                        dim3(32 * warps), 0, stream, (const T*)a, (const T*)g, ldg, (T*)out,
                                                        items, heads, dv, lambda, scale, eps));
@@ -744,9 +793,30 @@ __global__ void pair_rows_kernel(const float* __restrict__ a, const float* __res
     }
 }
 
+// widths that are multiples of four: four entries a thread
+template <typename T>
+__global__ void pair_rows_vec_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int64_t vecs,
+                                     int H4) {
+    pdl_wait();
+    pdl_trigger();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / (2 * H4);
+        const int c = (int)(i - t * 2 * H4);
+        const float4 v = *reinterpret_cast<const float4*>((c < H4 ? a + (t * H4 + c) * 4 : b + (t * H4 + c - H4) * 4));
+        Vec4<T>::store(out + i * 4, v);
+    }
+}
+
 extern "C" int acorn_pair_rows(const float* a, const float* b, void* out, int tokens, int H, int dtype, cudaStream_t stream) {
     const int64_t total = (int64_t)tokens * 2 * H;
     if (total <= 0) return 0;
+    if (H % 4 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const int64_t vecs = total / 4;
+        int64_t vb = (vecs + 255) / 256;
+        if (vb > 148 * 16) vb = 148 * 16;
+        ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(pair_rows_vec_kernel<T>, dim3((int)vb), dim3(256), 0, stream, a, b,
+                                                           (T*)out, vecs, H / 4));
+    }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(pair_rows_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, a, b,

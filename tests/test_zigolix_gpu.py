@@ -448,13 +448,14 @@ def test_score_maps_combined_normed_and_gated():
     o = ops()
     g = torch.Generator().manual_seed(1)
     for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
-        for T, H, dv in ((5, 3, 7), (33, 2, 96), (1, 1, 130)):
+        # (value rows that take the form with four entries a lane, with a gate that is and is not aligned, and others)
+        for T, H, dv, off in ((5, 3, 7, 11), (33, 2, 96, 11), (33, 2, 96, 12), (9, 4, 128, 8), (3, 1, 516, 4), (1, 1, 130, 11)):
             a = torch.randn(T, H, 2, dv, generator=g).to(dtype)
-            wide = torch.randn(T, 11 + H * dv, generator=g).to(dtype)
+            wide = torch.randn(T, off + H * dv, generator=g).to(dtype)
             lam, sc, eps = 0.83, 0.4, 1e-5
-            a64, g64 = a.double(), wide[:, 11:].double().view(T, H, dv)
+            a64, g64 = a.double(), wide[:, off:].double().view(T, H, dv)
             want = plain.unit_rms(a64[:, :, 0] - lam * a64[:, :, 1], eps) * sc * torch.sigmoid(g64)
-            got = o.diff_combine(a.view(T, -1).to(DEV), wide.to(DEV)[:, 11:], H, dv, lam, sc, eps)
+            got = o.diff_combine(a.view(T, -1).to(DEV), wide.to(DEV)[:, off:], H, dv, lam, sc, eps)
             assert (got.float().cpu().view(T, H, dv) - want).abs().max() < tol
             want = plain.unit_rms(a64[:, :, 0] - lam * a64[:, :, 1], eps) * sc
             got = o.diff_combine(a.view(T, -1).to(DEV), None, H, dv, lam, sc, eps)
@@ -534,9 +535,11 @@ def test_rotation_with_a_factor_then_unit_norm_and_keys_as_values():
 def test_pass_entry_kernels():
     o = ops()
     g = torch.Generator().manual_seed(5)
-    a, b = torch.randn(7, 12, generator=g), torch.randn(7, 12, generator=g)
-    for dtype in (torch.float32, torch.bfloat16):
-        got = o.pair_rows(a.to(DEV), b.to(DEV), dtype)
-        assert torch.equal(got.cpu(), torch.cat([a, b], 1).to(dtype))
+    for width in (12, 7, 256):
+        a, b = torch.randn(7, width, generator=g), torch.randn(7, width, generator=g)
+        for dtype in (torch.float32, torch.bfloat16):
+            got = o.pair_rows(a.to(DEV), b.to(DEV), dtype)
+            assert torch.equal(got.cpu(), torch.cat([a, b], 1).to(dtype))
+    a = torch.randn(7, 12, generator=g)
     row = torch.randn(12, generator=g)
     assert torch.equal(o.add_row(a.to(DEV).clone(), row.to(DEV)).cpu(), a + row)
