@@ -117,7 +117,7 @@ def _zigolix(width: int, vocab: int, heads: int, kv_heads: int, ff: int, window:
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": ff // (2 * top), "limit": 7.0}, "router": {"experts": experts, "top": top},
            "shared": {"ff": ff // 2, "limit": 7.0}}
-    dif = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 50.0, "diff": 0.6,
+    dif = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 30.0, "diff": 0.5,
            "mask": {"size": window}}
     att = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 1.0, "mask": {"size": window},
            "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
@@ -126,7 +126,7 @@ def _zigolix(width: int, vocab: int, heads: int, kv_heads: int, ff: int, window:
         layers.append({"type": "attention_2", "mixer": dict(dif), "mlp": dense})
         layers.append({"type": "attention_2", "mixer": dict(dif), "mlp": moe})
         layers.append({"type": "attention", "mixer": dict(att), "mlp": dense})
-    return {"architecture": "Zigolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+    return {"architecture": "Zigolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.7,
             "loop": {"start": 1, "stop": 3, "times": times}, "layers": layers}
 
 

@@ -97,6 +97,9 @@ def test_presets_of_the_family_are_valid_configurations():
             assert len(cfg.layers) == 10 and cfg.layers[4].mixer.kv_from == 1
         elif name.startswith("vagulorn"):
             assert [l.type for l in cfg.layers[:4]] == ["mamba2", "attention", "parallel", "mamba2"]
+        elif name.startswith("zigolix"):
+            assert [l.type for l in cfg.layers[:3]] == ["attention_2", "attention_2", "attention"]
+            assert len(spec_for(cfg).schedule) == 8          # layers 1 and 2 twice among six
         else:
             assert name.startswith("tedenex") and [l.type for l in cfg.layers[:3]] == ["wkv", "attention", "latent_attention"]
             assert len(spec_for(cfg).schedule) == 9          # the first three layers twice, then the other three

@@ -397,10 +397,10 @@ def test_attention_window_sink_cap_and_maps(dtype, tol, kernel, d, dv, nq, nkv, 
     serves them: a spiked key decides the result while it is inside the window (the last position that still
     sees it, at a page border, far back in a long row, in prompt rows and decoded tokens) and leaves it one
     position later; the sink takes weight from every key; the cap flattens the spike."""
-    P, Wn = 16, 40
-    befores = [0, 100, 2 * Wn - 1, 2 * Wn, 139, 140, Wn, 0]
+    P, Wn = 16, 36
+    befores = [0, 100, 2 * Wn - 1, 2 * Wn, 100 + Wn - 1, 100 + Wn, Wn, 0]
     qlens = [200, 70, 1, 1, 1, 1, 2, 1]
-    # row 4 (position 139) is the last to see key 100 under a window of 40; row 5 (position 140) the first not to
+    # row 4 (position 100 + Wn - 1) is the last to see key 100 under the window; row 5, one position on, the first not to
     spikes = [(0, 0), (0, 63), (0, 64), (0, 130), (1, 99), (1, 128), (2, Wn), (3, Wn), (4, 100), (5, 100), (6, 1), (6, 2)]
     sinks = torch.linspace(-1.0, 3.0, nq, dtype=torch.float64)
     got, want = _attention_case(befores, qlens, P, d, dv, nq, nkv, Wn, spikes, dtype, kernel, sinks, 30.0, maps)
@@ -423,8 +423,8 @@ def test_attention_window_sink_cap_and_maps(dtype, tol, kernel, d, dv, nq, nkv, 
 def test_sink_and_cap_in_the_tcgen05_prefill_kernel():
     """Key rows of 128: long rows on the tcgen05 kernel with a sink per head, capped scores and a window, a spiked key
     just inside and just outside it, beside short rows and decoded tokens on the other kernels."""
-    P, Wn, d, nq, nkv = 16, 40, 128, 8, 2
-    befores = [0, 100, 139, 140, 17]
+    P, Wn, d, nq, nkv = 16, 36, 128, 8, 2
+    befores = [0, 100, 100 + Wn - 1, 100 + Wn, 17]
     qlens = [200, 70, 1, 1, 40]
     spikes = [(0, 0), (0, 63), (0, 64), (0, 130), (1, 99), (1, 128), (2, 100), (3, 100), (4, 20)]
     sinks = torch.linspace(-1.0, 3.0, nq, dtype=torch.float64)

@@ -56,9 +56,9 @@ ZIG_B = dict(page_size=4, seed=32, cfg=ZigolixConfig(
 
 # sizes at which the bfloat16 engine takes its tensor-core paths (key rows that are multiples of 16, values as wide)
 ZIG_C = dict(page_size=16, seed=33, cfg=ZigolixConfig(
-    vocab_size=330, hidden_size=128, norm_eps=1e-5, logit_scale=0.5, loop=LayerLoop(1, 3, 2), layers=(
-        L(dif(heads=4, kv_heads=2, dim=32, vdim=64, scale=0.18, diff=0.6, softcap=20.0, mask=40), ff=192),
-        L(sink(heads=4, kv_heads=2, dim=64, scale=0.3, mask=50, rot=32, base=5e4, scaling=RotaryScaling(2.0, 128, 16.0, 1.0)),
+    vocab_size=330, hidden_size=128, norm_eps=1e-5, logit_scale=0.6, loop=LayerLoop(1, 3, 2), layers=(
+        L(dif(heads=4, kv_heads=2, dim=32, vdim=64, scale=0.18, diff=0.55, softcap=20.0, mask=36), ff=192),
+        L(sink(heads=4, kv_heads=2, dim=64, scale=0.3, mask=50, rot=32, base=2e4, scaling=RotaryScaling(2.5, 128, 16.0, 1.0)),
           ff=moe(64, 2.0, 8, 2, 64, 2.0)),
         L(dif(heads=2, kv_heads=1, dim=64, vdim=128, scale=0.12, diff=0.4, softcap=6.0, mask=100), ff=moe(32, 1.0, 6, 3)),
         L(sink(heads=8, kv_heads=1, dim=32, scale=0.4, mask=None, rot=32, base=1e4), ff=64),
@@ -105,12 +105,12 @@ def random_config(seed: int) -> ZigolixConfig:
             rot = rng.choice([0, d, d // 2, 16])
             sc = rng.choice([None, RotaryScaling(rng.choice([2.0, 8.0]), rng.choice([64, 256]), rng.choice([32.0, 8.0]), 1.0)])
             layers.append(L(sink(heads, kv, d, d ** -0.5 * 4, mask=rng.choice([None, 32, 64, 100, 256]), rot=rot,
-                                 base=rng.choice([1e4, 5e4, 1e6]), scaling=sc if rot else None), ff))
+                                 base=rng.choice([1e4, 2e5, 1e6]), scaling=sc if rot else None), ff))
         else:
             d = rng.choice([16, 32, 48, 64, 24])
             dv = rng.choice([2 * d, 2 * d, d, 48])
             layers.append(L(dif(heads, kv, d, dv, d ** -0.5, diff=rng.choice([0.2, 0.5, 0.8]),
-                                softcap=rng.choice([None, 5.0, 50.0]), mask=rng.choice([None, 24, 40, 128])), ff))
+                                softcap=rng.choice([None, 5.0, 30.0]), mask=rng.choice([None, 24, 36, 128])), ff))
     start = rng.randrange(n)
     stop = rng.randint(start + 1, n)
     return ZigolixConfig(vocab_size=rng.choice([300, 520, 1000]), hidden_size=width, norm_eps=rng.choice([1e-5, 1e-6]),
