@@ -11,6 +11,11 @@
 // second kernel merges the splits.  Why mma.sync and not tcgen05: the useful M is rep (4 at
 // Qwen3-8B sizes), far below a tcgen05 tile, and the kernel is bound by reading K and V once.
 //
+// Options: a cap c on the scaled scores (c tanh(score / c), by the fast exponential and quotient); a sink per head
+// (exp(sink) in the softmax denominator, no key, no value: split 0 adds it, so that the merge counts it once); several
+// score maps side by side in a head (the (head, map) pairs are the rows of the tile, a pair's query laid out with
+// zeros outside its map's entries of the key row: see attention_plain.cu).
+//
 // Reference for the split/merge scheme: acorninfer/ops/paged_attention.py:33-122 (one query
 // head per program there, so K/V were read rep times).
 #include "mma_helpers.cuh"

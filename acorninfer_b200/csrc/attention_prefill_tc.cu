@@ -15,7 +15,10 @@
 //              with tcgen05.st.  O stays in tensor memory across blocks; it is rescaled
 //              (tcgen05.ld / st) only when a row's maximum has grown by more than 2^8 since its
 //              reference was set, so most blocks skip that pass.  At the end the thread reads
-//              its row of O, divides by the row sum and writes the output.
+//              its row of O, divides by the row sum and writes the output.  Options of the scores:
+//              a penalty per head on the distance to the key, a cap c (c tanh(score / c), two more
+//              special-function operations a score), a sink per head (exp(sink) joins the row sum
+//              at the end, against the same reference maximum).
 //   warp 8     producer: TMA loads of Q (once) and of the K and V tiles of each block
 //              ((page, kv head) tiles are contiguous [page_size x 128] in the cache) into a ring
 //              of five 32 KB slots, K_0 V_0 K_1 V_1 ..., so that loads run two blocks ahead.

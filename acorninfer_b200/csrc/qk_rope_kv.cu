@@ -10,6 +10,10 @@
 //   q is written back in place; k goes to the K page, v (untouched) to the V page.
 // Cache layout per layer: [num_pages, nkv, page_size, d]; the token at position p of
 // row r lives in page block_table[r * table_stride + p / P - page_base[r]], slot p % P.
+// `magnitude` multiplies cos and sin (position encodings with stretched frequencies).  With norm_after the
+// order is the other way round: the head is rotated first and then brought to unit root mean square,
+// x <- x * rsqrt(mean(x^2) + eps) over rotated and unrotated entries alike (times w if a weight is given,
+// no weight otherwise); both are the general kernel's.
 // With write_kv = 0 only the query heads are processed (a layer that reads another
 // layer's cache).  Value heads may have a width of their own (dv; their pages then hold rows of dv),
 // a row of qkv may be wider than its heads (ld elements), and with v_from_k the values are the keys as
