@@ -255,6 +255,35 @@ def test_preemption_recomputes_float32(case):
         assert len(a) == len(p) + 16 and follows_plain(cfg, w, p, a, 1e-4)
 
 
+def test_trace_run_program_serves_the_design(tmp_path):
+    """``bin/trace_run`` as a program on a Zigolix folder: it picks the model by ``config.json``, runs a mixed trace in
+    a pool sized for the live requests and writes the logits asked for."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    tiny = ZIGS["zig_b"]
+    d = make_model_dir(tmp_path / "model", tiny)
+    reqs = {f"t{i}": random_tokens(n, tiny["cfg"].vocab_size, 300 + i) for i, n in enumerate([35, 48, 21, 66, 40])}
+    ref = plain_logits(tiny["cfg"], read_weights(d), reqs)
+    steps = traces.mixed(reqs, seed=4)
+    out = tmp_path / "out"
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run(
+        [sys.executable, str(root / "bin" / "trace_run"), "--model", str(d), "--dtype", "float32", "--out", str(out),
+         "--max-tokens", str(traces.max_live_tokens(steps))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    V = tiny["cfg"].vocab_size
+
+    def read_step(msg):
+        f = out / f"{msg['step']}.f32"
+        return np.fromfile(f, dtype="<f4").reshape(-1, V) if f.exists() else None
+
+    check(traces.collect(read_step, steps), ref, "float32", "trace_run")
+
+
 # ------------------------------------------------------------------ one mechanism at a time
 
 
