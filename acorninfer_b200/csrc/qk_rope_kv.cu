@@ -165,6 +165,70 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
     for (int i = rot + lane; i < d; i += 32) dst[i] = from_float<T>(x[i]);
 }
 
+// Rotation of neighbouring pairs, then the norm (norm_after), for heads of up to 128 entries that are multiples of four:
+// a warp a (token, head), four consecutive entries a lane (8- or 16-byte accesses), which are two whole pairs, so that
+// rotation, sum of squares and write need neither shared memory nor a second pass.  Value heads are the key heads as
+// projected (v_from_k) or columns of their own.
+template <typename T>
+__global__ void qk_rope_norm_after_vec_kernel(T* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                                              const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                              const int* __restrict__ token_row, const int* __restrict__ block_table,
+                                              const int* __restrict__ page_base, int table_stride, T* __restrict__ k_pages,
+                                              T* __restrict__ v_pages, int tokens, int nq, int nkv, int d, int rot, int P,
+                                              float eps, int write_kv, int64_t ld, int v_from_k, float magnitude) {
+    pdl_wait();
+    pdl_trigger();
+    const int warps_per_block = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = write_kv ? (nq + 2 * nkv) : nq;
+    const int64_t item = (int64_t)blockIdx.x * warps_per_block + warp;
+    if (item >= (int64_t)tokens * heads) return;
+    const int t = (int)(item / heads);
+    const int h = (int)(item - (int64_t)t * heads);
+    const int pos = positions[t];
+    const int i = 4 * lane;                                              // this lane's first entry
+    const bool live = i < d;
+    const T* src = qkv + (int64_t)t * ld + (int64_t)h * d;
+    T* dst = qkv + (int64_t)t * ld + (int64_t)h * d;                     // q: in place
+    if (h >= nq) {
+        const int r = token_row[t];
+        const int kvh = (h - nq) % nkv;
+        const int page = block_table[(int64_t)r * table_stride + (pos / P - page_base[r])];
+        const int64_t slot = ((int64_t)page * nkv + kvh) * P + (pos % P);
+        dst = ((h < nq + nkv) ? k_pages : v_pages) + slot * d;
+        if (h >= nq + nkv) src = qkv + (int64_t)t * ld + (v_from_k ? (int64_t)(nq + kvh) * d : (int64_t)(nq + nkv + kvh) * d);
+    }
+    float4 x = live ? Vec4<T>::load(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (h >= nq + nkv) {                                                 // a value head: as projected
+        if (live) Vec4<T>::store(dst + i, x);
+        return;
+    }
+    if (live && i < rot) {                                               // pairs (i, i + 1) and, if rotated too, (i + 2, i + 3)
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
+        sn *= magnitude;
+        cs *= magnitude;
+        const float a = x.x, b = x.y;
+        x.x = a * cs - b * sn;
+        x.y = b * cs + a * sn;
+        if (i + 2 < rot) {
+            sincosf((float)pos * inv_freq[(i >> 1) + 1], &sn, &cs);
+            sn *= magnitude;
+            cs *= magnitude;
+            const float c = x.z, e = x.w;
+            x.z = c * cs - e * sn;
+            x.w = e * cs + c * sn;
+        }
+    }
+    const float ss = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+    const float inv = rsqrtf(ss / (float)d + eps);
+    const float* w = (h < nq) ? q_w : k_w;
+    if (live) {
+        const float4 wv = w ? *reinterpret_cast<const float4*>(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        Vec4<T>::store(dst + i, make_float4(x.x * inv * wv.x, x.y * inv * wv.y, x.z * inv * wv.z, x.w * inv * wv.w));
+    }
+}
+
 // The same for the common case (whole head rotated, half pairing, head size 16, 32, 64, 128 or
 // 256): a group of d / 8 lanes takes ROPE_HPG consecutive heads of one token, each lane holding
 // four rotary pairs (x[4l .. 4l+3], x[d/2 + 4l .. d/2 + 4l+3]) of every head in registers; vector
@@ -445,6 +509,15 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
             default: ROPE_VEC(32); break;
         }
 #undef ROPE_VEC
+    }
+    if (plain_rows && norm_after && pairing == 1 && d % 4 == 0 && d <= 128 && dv == d && ld % 4 == 0 && qk_aligned16(qkv) &&
+        qk_aligned16(k_pages) && qk_aligned16(v_pages) && qk_aligned16(q_w) && qk_aligned16(k_w)) {
+        const int warps = 4;
+        const int64_t items = (int64_t)tokens * (write_kv ? (nq + 2 * nkv) : nq);
+        ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(
+            qk_rope_norm_after_vec_kernel<T>, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream,
+            (T*)qkv, q_w, k_w, inv_freq, positions, token_row, block_table, page_base, table_stride, (T*)k_pages,
+            (T*)v_pages, tokens, nq, nkv, d, rot, P, eps, write_kv, ld, v_from_k, magnitude));
     }
     const int vec_taps = conv_w ? taps : 0;
     if (!plain_rows && !special && rot == 0 && !v_from_k && vec_taps <= 4 && d % 4 == 0 && dv % 4 == 0 && d <= 128 && dv <= 128 &&

@@ -529,7 +529,9 @@ def test_rotation_with_a_factor_then_unit_norm_and_keys_as_values():
     g = torch.Generator().manual_seed(4)
     P = 4
     for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
-        for nq, nkv, d, rot in ((3, 1, 10, 4), (4, 2, 32, 32), (2, 2, 130, 64), (1, 1, 8, 0)):
+        # (heads that take the form with four entries a lane: multiples of four up to 128; and others)
+        for nq, nkv, d, rot in ((3, 1, 10, 4), (4, 2, 32, 32), (2, 2, 130, 64), (1, 1, 8, 0), (2, 1, 128, 64), (4, 2, 64, 14),
+                                (3, 3, 20, 2), (1, 1, 96, 96)):
             befores, qlens = [5, 0, 9], [7, 3, 1]
             lay = rows_layout(befores, qlens, P, 12, seed=d)
             T = lay["num_tokens"]
